@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the fused MXFP4 MoE layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4] [--impl reference]
+
+One step = one pass of the hot path (route -> align -> gate/up GEMM + activation -> down GEMM with
+fused weighted combine) over one batch of seeded synthetic tokens. Default workload: the
+gpt-oss-120b-shaped prefill layer (H = I = 2880, E = 128, top-4, T = 8192), the configuration the
+headline metric is quoted on at 1, 2, 4 and 8 GPUs; with --gpus N > 1 (launched under torchrun)
+the experts are partitioned over the ranks and tokens travel by NCCL all-to-all (strong scaling:
+the global batch is fixed). The same JSON line also carries the single-GPU decode sweep of the
+gpt-oss-20b-shaped layer (T in 1..128) with its HBM roofline.
+
+Prints ONE JSON line on rank 0. `--impl reference` times the reference's own CPU implementation
+of the path (oracle/_ref, else the C restatement) on the host cores over a bounded token sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from vkernels_b200 import synthetic as syn  # noqa: E402
+
+METRIC = "MXFP4 MoE layer tokens/s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        reasons = []
+        for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
+            if any(r[3 + i] == "Active" for r in self.rows):
+                reasons.append(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.rows[0][1]),
+                "power_w_max": max(float(r[2]) for r in self.rows), "samples": len(self.rows), "reasons": reasons}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own implementation of the path on a bounded token sample
+# ------------------------------------------------------------------------------------------------
+
+def cpu_sample_rate(cfg, n_tokens, n_experts_gen, repeats=1, prefer_reference=True):
+    """tokens/s of the CPU path (route restatement + reference layer) on `n_tokens` seeded tokens.
+    Weights of `n_experts_gen` experts are generated; routing is over those experts."""
+    import oracle
+
+    oracle.build()
+    small = syn.scaled(cfg, E=n_experts_gen, n_group=1, topk_group=1) if n_experts_gen != cfg.E else cfg
+    w = {k: v.numpy() for k, v in syn.make_expert_weights(small, n_experts=small.n_weight_experts).items()}
+    A = syn.make_activations(small, n_tokens)
+    Au = A.view(torch.int16).numpy().view(np.uint16)
+    r = syn.make_router(small)
+    cores = os.cpu_count() or 1
+    kind = "reference" if (prefer_reference and oracle.have_reference()) else "port"
+    oracle.set_num_threads(cores)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        logits = oracle.router_logits(Au, r["wr"].numpy())
+        if small.routing == "sigmoid_group":
+            ids, tw, _ = oracle.route_sigmoid_group_topk(logits, r["bias"].numpy(), small.top_k, scaling=small.scaling)
+        else:
+            ids, tw, _ = oracle.route_softmax_topk(logits, small.top_k)
+        if small.shared_experts:
+            ids = np.concatenate([ids, np.full((n_tokens, 1), small.E, np.int32)], 1)
+            tw = np.concatenate([tw, np.ones((n_tokens, 1), np.float32)], 1)
+        oracle.moe_layer(Au, w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], ids, tw,
+                         num_experts=small.n_weight_experts, swiglu_limit=small.swiglu_limit, impl=kind,
+                         threads=cores if kind == "reference" else 0)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": n_tokens / best, "unit": UNIT, "cores": cores, "kind": kind, "seconds": best,
+            "sample": f"{n_tokens} seeded tokens of the workload routed over {n_experts_gen} of its experts "
+                      f"(same H, I, top_k); one pass of router + layer on all {cores} host threads"}
+
+
+def run_reference_arm(args, cfg, T):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_tok = min(T, args.cpu_tokens)
+    n_exp = min(cfg.E, 16)
+    for _ in range(args.warmup and 1):
+        cpu_sample_rate(cfg, min(n_tok, 16), n_exp)
+    vals = [cpu_sample_rate(cfg, n_tok, n_exp) for _ in range(max(1, min(args.steps, 3)))]
+    best = max(vals, key=lambda v: v["value"])
+    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": 1, "ms_per_step": best["seconds"] * 1e3 * T / n_tok,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32",
+            "data": "synthetic", "config": workload_config(cfg, T, args.gpus),
+            "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, T, n_gpus):
+    return {"workload": f"{cfg.name}: T={T} H={cfg.H} I={cfg.I} E={cfg.E}+{cfg.shared_experts} top{cfg.top_k} "
+                        f"{cfg.routing}", "tokens": T, "hidden": cfg.H, "ispp": cfg.I, "experts": cfg.E,
+            "top_k": cfg.top_k, "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus} (experts split, NCCL all-to-all)",
+            "weights": "MXFP4, 12 finite E2M1 codes uniform, ue8m0 exponent uniform in "
+                       f"[{cfg.scale_exp[0]},{cfg.scale_exp[1]}]",
+            "l2": "expert weights touched per step exceed the 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+
+def time_steps(fn, steps, warmup, barrier=None):
+    """CUDA-event time of `steps` calls of fn after `warmup` untimed ones; returns per-step ms list."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+
+
+def kernel_times(fn, calls):
+    """Average device time (ms) of the gate/up and the down kernel over `calls` layer calls."""
+    import ctypes
+
+    from vkernels_b200 import native_runtime as nr
+
+    lib = nr.load_library()
+    nr.check(lib.vk_cuda_moe_timing_begin(calls), "timing_begin")
+    for _ in range(calls):
+        fn()
+    g, d, n = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+    nr.check(lib.vk_cuda_moe_timing_end(ctypes.byref(g), ctypes.byref(d), ctypes.byref(n)), "timing_end")
+    return g.value / max(n.value, 1), d.value / max(n.value, 1), n.value
+
+
+def launches_per_step(T, slots):
+    """Kernels of this library per layer call: router logits + top-k, alignment (1 kernel up to
+    1024 routed slots, else 3), tile list, row gather, gate/up GEMM, down GEMM."""
+    return 2 + (1 if T * slots <= 1024 else 3) + 4
+
+
+def decode_sweep(peaks, steps, warmup):
+    """gpt-oss-20b-shaped layer, T in {1, 8, 32, 64, 128}: tokens/s and HBM roofline fraction on the
+    weight bytes of the experts the batch touches (+ activations, output, router weight)."""
+    from vkernels_b200.experts import layer_from_config
+
+    cfg = syn.CONFIGS["c1"]
+    dev = "cuda:0"
+    # several weight copies so that a small batch cannot live in L2 between steps
+    n_copies = 3
+    layers = []
+    r = syn.make_router(cfg, device=dev)
+    for c in range(n_copies):
+        w = syn.make_expert_weights(cfg, seed=cfg.seed + 17 * c, backend="torch", device=dev)
+        layers.append(layer_from_config(cfg, w, r, max_tokens=128))
+    out = []
+    for T in cfg.T:
+        A = syn.make_activations(cfg, T, backend="torch", device=dev)
+        ids, _ = layers[0].route(A)
+        touched = int(torch.unique(ids).numel())
+        state = {"i": 0}
+
+        def step():
+            layers[state["i"] % n_copies](A)
+            state["i"] += 1
+
+        ms = time_steps(step, max(steps, 20), max(warmup, 5))
+        med = statistics.median(ms)
+        bytes_alg = syn.decode_algorithmic_bytes(cfg, T, touched)
+        gbs = bytes_alg / (med * 1e-3) / 1e9
+        out.append({"T": T, "experts_touched": touched, "ms_per_step": med, "ms_min": min(ms),
+                    "tokens_per_s": T / (med * 1e-3), "algorithmic_bytes": bytes_alg, "achieved_gbs": gbs,
+                    "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8tbs": gbs / 8000.0})
+    return out
+
+
+def run_single_gpu(args, cfg, T):
+    from vkernels_b200 import torch_ops as ops
+    from vkernels_b200.experts import layer_from_config
+
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    w = syn.make_expert_weights(cfg, backend="torch", device=dev)
+    r = syn.make_router(cfg, device=dev)
+    A = syn.make_activations(cfg, T, backend="torch", device=dev)
+    logits = syn.make_zipf_logits(cfg, T, device=dev) if cfg.zipf_alpha else None
+    layer = layer_from_config(cfg, w, r, max_tokens=T)
+    step = (lambda: layer(A, logits=logits))
+
+    with ClockSampler(0) as clk:
+        ms = time_steps(step, args.steps, args.warmup)
+    clocks = clk.summary()
+    ops.kernel_status()
+    total_ms = sum(ms)
+    ms_per_step = total_ms / args.steps
+    value = T / (ms_per_step * 1e-3)
+
+    g_ms, d_ms, n_calls = kernel_times(step, max(3, min(args.steps, 10)))
+    flops_gateup = 4 * T * cfg.slots * cfg.I * cfg.H
+    flops_down = 2 * T * cfg.slots * cfg.I * cfg.H
+    tensor_peak = peaks["bf16_tflops_sustained"]
+    achieved = flops_gateup / (g_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "moe_gemm_sm100_kernel<gate/up>", "achieved": achieved,
+                "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
+                "traffic": None, "algorithmic_flops_per_launch": flops_gateup, "ms_per_launch": g_ms,
+                "down_kernel": {"achieved": flops_down / (d_ms * 1e-3) / 1e12, "ms_per_launch": d_ms,
+                                "frac": flops_down / (d_ms * 1e-3) / 1e12 / tensor_peak},
+                "layer": {"achieved": cfg.flops(T) / (ms_per_step * 1e-3) / 1e12,
+                          "frac": cfg.flops(T) / (ms_per_step * 1e-3) / 1e12 / tensor_peak}}
+
+    # end to end: pinned host activations in, pinned host bf16 result out, copies inside the region
+    xh = A.cpu().pin_memory()
+    yh = torch.empty((T, cfg.H), dtype=torch.bfloat16).pin_memory()
+    if logits is None:
+        e2e_step = lambda: layer.forward_host(xh, yh)
+        for _ in range(args.warmup):
+            e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        e2e = {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.H * 2,
+               "d2h_bytes_per_step": T * cfg.H * 2, "ms_per_step": e2e_ms}
+    else:
+        e2e = None
+
+    cpu = cpu_sample_rate(cfg, min(T, args.cpu_tokens), min(cfg.E, 16))
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "ms_per_step_min": min(ms), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32", "data": "synthetic",
+            "config": workload_config(cfg, T, 1), "roofline": roofline,
+            "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}, "e2e": e2e,
+            "gpu_launches": launches_per_step(T, cfg.slots) * args.steps, "clocks": clocks}
+    if args.decode_sweep:
+        del layer, w
+        torch.cuda.empty_cache()
+        line["decode_sweep"] = {"workload": syn.describe(syn.CONFIGS["c1"]), "bound": "hbm",
+                                "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                                "points": decode_sweep(peaks, args.steps, args.warmup)}
+    print(json.dumps(line), flush=True)
+
+
+def run_multi_gpu(args, cfg, T):
+    import torch.distributed as dist
+
+    from vkernels_b200.dist import ExpertParallelMoE
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist.init_process_group("nccl", device_id=torch.device(dev))
+    layer = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T // world)
+    T_local = T // world
+    A = syn.make_activations(cfg, T, backend="torch", device=dev, seed=cfg.seed)[rank * T_local:(rank + 1) * T_local].contiguous()
+    step = lambda: layer(A)
+    barrier = lambda: dist.barrier()
+    with ClockSampler(local) as clk:
+        ms = time_steps(step, args.steps, args.warmup, barrier=barrier)
+    t = torch.tensor([sum(ms)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    stats = layer.last_stats()
+    if rank == 0:
+        line = {"metric": METRIC, "value": T / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32", "data": "synthetic",
+                "config": workload_config(cfg, T, world), "roofline": None, "cpu_baseline": None,
+                "e2e": None, "gpu_launches": stats["launches_per_step"] * args.steps, "clocks": clk.summary(),
+                "ep": stats}
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=list(syn.CONFIGS))
+    ap.add_argument("--tokens", type=int, default=0, help="override the batch size of the workload")
+    ap.add_argument("--cpu-tokens", type=int, default=256, help="token sample of the CPU baseline")
+    ap.add_argument("--no-decode-sweep", dest="decode_sweep", action="store_false")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    cfg = syn.CONFIGS[args.workload]
+    T = args.tokens or max(cfg.T)
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, T)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        run_multi_gpu(args, cfg, T)
+    else:
+        run_single_gpu(args, cfg, T)
+
+
+if __name__ == "__main__":
+    main()

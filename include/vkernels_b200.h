@@ -1,0 +1,185 @@
+/* vkernels_b200.h - C ABI of libvkernels_b200.so: the fused MXFP4
+ * mixture-of-experts layer for NVIDIA B200 (sm_100a).
+ *
+ * The first group of entry points keeps the names, argument lists and error
+ * behaviour of the reference library's entry points for this path, so a loader
+ * written against the reference binds them unchanged; each comment names the
+ * reference declaration it replaces (paths relative to the reference tree).
+ * The vk_cuda_* group is additive.
+ *
+ * Conventions (reference src/c/vkernels/capi/capi.hpp:41-68): int-returning
+ * functions return VK_OK or a VK_ERROR_* code and leave a message readable
+ * through vk_last_error() on the calling thread; nothing throws across this
+ * boundary. Device entry points take DEVICE pointers, enqueue on `stream`
+ * (NULL = default stream) and return without synchronising. */
+#ifndef VKERNELS_B200_H_
+#define VKERNELS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes - capi.hpp:41-47. */
+enum {
+  VK_OK = 0,
+  VK_ERROR_INVALID_ARGUMENT = 1,
+  VK_ERROR_OUT_OF_RANGE = 2,
+  VK_ERROR_UNSUPPORTED = 3,
+  VK_ERROR_INTERNAL = 4
+};
+
+/* capi.hpp:53-68. */
+const char* vk_version(void);
+int vk_has_cuda(void);
+const char* vk_last_error(void);
+int vk_last_error_code(void);
+void vk_set_last_error(int code, const char* message);
+
+/* ---- device entry points (DEVICE pointers) ------------------------------ */
+
+/* Replaces vk_hip_fused_moe_mxfp4 - src/c/vkernels/capi/hip_capi.hpp:99-108
+ * (C++ launcher src/c/vkernels/kernels/moe_fused.hpp:322-344).
+ *   A [M,hidden] bf16; w13 [E,2*ispp,hidden/2] packed E2M1, gate rows then up
+ *   rows; w13_scale [E,2*ispp,hidden/32] ue8m0; w2 [E,hidden,ispp/2];
+ *   w2_scale [E,hidden,ispp/32]; topk_ids unused by the kernels (kept for the
+ *   signature); topk_w [M*top_k] read at the flat index; act_scratch
+ *   [EM,ispp] bf16, padding rows never written; out [M,hidden] fp32,
+ *   ACCUMULATED INTO - zero it first; sorted_ids [EM], expert_ids
+ *   [EM/block_size] as produced by the alignment; activation 0 = SwiGLU
+ *   (clamped at swiglu_limit when > 0), 1 = SiTU(beta, linear_beta);
+ *   b13 [E,2*ispp] / b2 [E,hidden] fp32 or NULL; block_size = alignment
+ *   granularity (any multiple of 16; 16 packs best on this implementation).
+ * void like the reference: a contract violation leaves a message in
+ * vk_last_error() and launches nothing. */
+void vk_hip_fused_moe_mxfp4(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                            const uint8_t* w2, const uint8_t* w2_scale, const int32_t* topk_ids,
+                            const float* topk_w, uint16_t* act_scratch, float* out, int M,
+                            int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                            const int32_t* expert_ids, int EM, float swiglu_limit, int activation,
+                            float beta, float linear_beta, const float* b13, const float* b2,
+                            int block_size, void* stream);
+
+/* Replaces vk_hip_moe_align_block_size - hip_capi.hpp:148-153 (kernel
+ * src/c/vkernels/kernels/moe_fused.hip:1983-2099). Same outputs, bit for bit,
+ * as the host alignment (src/c/vkernels/kernels/moe_fused.cpp:609-661) for any
+ * N = M*top_k: the reference's N <= 1024 limit (VK_ERROR_UNSUPPORTED) is gone.
+ * expert_map [num_experts] global->local (-1 = skip) or NULL. All max_EM
+ * entries of sorted_ids and max_EM/block_size of expert_ids are written;
+ * *out_EM (device) receives the padded row count, block_size when nothing
+ * routes. */
+int vk_hip_moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, int32_t M,
+                                int32_t top_k, int32_t block_size, int32_t num_experts,
+                                int32_t local_n, int32_t max_EM, int32_t* sorted_ids,
+                                int32_t* expert_ids, int32_t* out_EM, void* stream);
+
+/* ---- host entry points (HOST pointers) ----------------------------------- */
+
+/* Replaces vk_fused_moe_mxfp4 - capi.hpp:515-524 (capi_moe.cpp:81-108), whose
+ * body is the CPU oracle. Here every buffer is copied to the GPU, the CUDA
+ * kernels run and act_scratch/out are copied back; the call synchronises.
+ * topk_w_sorted [EM] is in sorted-row order; expert_ids is per 16 rows;
+ * group_size must be 32. */
+int32_t vk_fused_moe_mxfp4(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                           const uint8_t* w2, const uint8_t* w2_scale, const int32_t* sorted_ids,
+                           const float* topk_w_sorted, const int32_t* expert_ids,
+                           uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
+                           int top_k, int EM, int group_size, float swiglu_limit, int activation,
+                           float beta, float linear_beta, const float* b13, const float* b2);
+
+/* Replaces vk_moe_align_block_size - capi.hpp:530-533 (capi_moe.cpp:119-140):
+ * host buffers, GPU execution, host contract (*out_EM = 0 when nothing
+ * routes; only the first *out_EM entries are written). */
+int32_t vk_moe_align_block_size(const int32_t* topk_ids, int32_t M, int32_t top_k,
+                                int32_t block_size, int32_t num_experts, int32_t* sorted_ids,
+                                int32_t* expert_ids, int32_t* out_EM);
+
+/* capi.hpp:537-539 (capi_moe.cpp:110-117). */
+size_t vk_moe_align_block_size_max_em(int32_t M, int32_t top_k, int32_t block_size,
+                                      int32_t num_experts);
+
+/* ---- additive entry points (DEVICE pointers) ------------------------------ */
+
+/* The layer with routing weights already in sorted-row order (the CPU entry
+ * point's convention, moe_fused.hpp:83-101) - no reference counterpart on the
+ * device side. */
+int vk_cuda_fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13,
+                                     const uint8_t* w13_scale, const uint8_t* w2,
+                                     const uint8_t* w2_scale, const float* topk_w_sorted,
+                                     uint16_t* act_scratch, float* out, int M, int hidden,
+                                     int ispp, int top_k, const int32_t* sorted_ids,
+                                     const int32_t* expert_ids, int EM, float swiglu_limit,
+                                     int activation, float beta, float linear_beta,
+                                     const float* b13, const float* b2, int block_size,
+                                     void* stream);
+
+/* Router. The reference has no router in this path; semantics follow its GPU
+ * routing ops (src/python/vkernels/torch_ops/tokenspeed_amd/routing.py:58-145,
+ * torch_ops/glm_router.py:43-88,184-262).
+ * logits[T,E] = bf16 x[T,H] . fp32 wr[E,H]^T, fp32 accumulation. */
+int vk_cuda_moe_router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H,
+                              int E, void* stream);
+/* sigmoid = 0: softmax scores, selection on score (+ bias), weights = scores,
+ * renorm divides by the selected sum (0 -> 1). sigmoid = 1: selection on
+ * sigmoid + bias, weights = unbiased sigmoid, renorm divides by sum + 1e-20;
+ * n_group > 1 keeps the topk_group groups with the largest sum of their two
+ * best biased scores. Ties go to the lowest index; ids are in descending
+ * selection order. ids/w are [T, k + n_shared]; trailing shared slots carry
+ * ids E, E+1, ... and weight 1. */
+int vk_cuda_moe_route_topk(const float* logits, const float* bias, int T, int E, int k,
+                           int sigmoid, int n_group, int topk_group, int renorm, float scaling,
+                           int n_shared, int32_t* ids, float* w, void* stream);
+
+/* 0 = tcgen05 tensor-core kernels (default), 1 = CUDA-core cross-check kernels
+ * that add in the CPU oracle's order. Also settable with VK_MOE_IMPL=simt. */
+int vk_cuda_moe_set_impl(int impl);
+int vk_cuda_moe_get_impl(void);
+
+/* The library keeps one grow-only scratch block per device (alignment
+ * histograms, tile lists, gathered activation rows). Growing it calls
+ * cudaMalloc: reserve the largest problem once, before any stream capture. */
+size_t vk_cuda_moe_workspace_bytes(int max_EM, int hidden, int ispp, int n_local_experts, int N);
+int vk_cuda_moe_reserve_workspace(size_t bytes);
+
+/* Synchronises the device and reports whether any tensor-core launch gave up
+ * on one of its bounded waits (VK_ERROR_INTERNAL) - never expected. */
+int vk_cuda_moe_kernel_status(void);
+
+/* Device time of the two GEMM kernels, measured with events on the launch
+ * stream around up to max_calls layer calls; _end synchronises and returns the
+ * summed milliseconds (the reference's VK_MOE_KTIME=1 prints the same split,
+ * src/c/vkernels/kernels/moe_fused.hip:1482-1493, but serialises the stages). */
+int vk_cuda_moe_timing_begin(int max_calls);
+int vk_cuda_moe_timing_end(float* gateup_ms, float* down_ms, int* calls);
+
+/* out[rows,K] bf16 = dequantised packed[rows,K/2] x scale[rows,K/32], through
+ * the device function the GEMM kernels use (reference definition
+ * moe_fused.cpp:141-174). */
+int vk_cuda_mxfp4_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
+                               int rows, int K, void* stream);
+
+/* Expert parallelism (partition rule: src/c/vkernels/dist/dist_moe.cpp:225-274).
+ * expert_begin [world+1]: first expert of each rank, last entry = E.
+ * phase 0: cursor[d] += number of tokens that must visit rank d (cursor zeroed
+ *          by the caller).
+ * phase 1: cursor[d] = first row of rank d's segment of the send buffers; each
+ *          visiting token takes the next row: send_x[row,:] = x[t,:],
+ *          send_ids/send_w [row, k + n_shared] = LOCAL expert id / weight of
+ *          the slots rank d owns (-1 / 0 elsewhere; shared slots only for
+ *          d == rank), row_of[t, d] = row or -1. */
+int vk_cuda_moe_ep_pack(const uint16_t* x, const int32_t* topk_ids, const float* topk_w, int T,
+                        int H, int k, int n_shared, int world, int rank,
+                        const int32_t* expert_begin, int32_t* cursor, int32_t* row_of,
+                        uint16_t* send_x, int32_t* send_ids, float* send_w, int phase,
+                        void* stream);
+/* out[t,:] = sum over ranks d ascending of recv_rows[row_of[t,d], :]; either
+ * output may be NULL. */
+int vk_cuda_moe_ep_combine(const float* recv_rows, const int32_t* row_of, int T, int H, int world,
+                           uint16_t* out_bf16, float* out_f32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VKERNELS_B200_H_ */

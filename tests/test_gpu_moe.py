@@ -1,0 +1,257 @@
+"""-m gpu: the fused layer through the C ABI against the CPU oracle.
+
+Gate (the layer's stated tolerance): outputs rounded to bf16, max-abs <= 2e-2 and relative L2
+<= 1e-2 against the oracle; NaN / inf masks must be equal. The CUDA-core cross-check path
+("simt") adds in the oracle's order and is held to a much tighter bound."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import oracle  # noqa: E402
+from gpu_common import DEV, gpu_layer, make_case, oracle_layer, oracle_route, to_np  # noqa: E402
+from helpers import (assert_close_bf16, bf2f, bf16_to_u16, expand_expert_ids, pack_pair, u16_to_bf16,  # noqa: E402
+                     uniform_problem)
+from vkernels_b200 import native_runtime as nr  # noqa: E402
+from vkernels_b200 import synthetic as syn  # noqa: E402
+from vkernels_b200 import torch_ops as ops  # noqa: E402
+from vkernels_b200.experts import layer_from_config  # noqa: E402
+
+IMPLS = ["simt", "tcgen05"]
+
+
+def run_uniform(impl, prob, sorted_ids, ws, eids, top_k=1, out_init=0.0, **kw):
+    """Known-answer problems take explicit sorted_ids / sorted weights: use the sorted-weight
+    entry point, as the CPU entry point does."""
+    A, w13, w13s, w2, w2s = prob
+    M, H = A.shape
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    out = torch.full((M, H), out_init, dtype=torch.float32, device=DEV)
+    act = torch.zeros((len(sorted_ids), w13.shape[1] // 2), dtype=torch.bfloat16, device=DEV)
+    b13, b2 = kw.pop("b13", None), kw.pop("b2", None)
+    ops.set_impl(impl)
+    try:
+        ops.fused_moe_mxfp4_into(out, act, u16_to_bf16(A, DEV), t(w13), t(w13s), t(w2), t(w2s),
+                                 t(np.asarray(ws, np.float32)), t(np.asarray(sorted_ids, np.int32)),
+                                 t(np.asarray(eids, np.int32)), top_k=top_k, weights_sorted=True,
+                                 b13=None if b13 is None else t(b13), b2=None if b2 is None else t(b2), **kw)
+        torch.cuda.synchronize()
+        ops.kernel_status()
+    finally:
+        ops.set_impl("tcgen05")
+    return to_np(out), bf16_to_u16(act)
+
+
+IDENT = (np.arange(16), np.ones(16), np.zeros(1))
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_tiny_bias_clamp_situ(impl):
+    """reference tests/kernels/moe/test_moe_fused.cpp:71-282."""
+    out, act = run_uniform(impl, uniform_problem(), *IDENT)
+    exp_act = 128.0 / (1.0 + math.exp(-128.0)) * 128.0
+    assert np.max(np.abs(out - exp_act * 64) / (exp_act * 64)) < 1e-2 and np.max(np.abs(bf2f(act) - exp_act)) < 0.5
+    b13 = np.concatenate([np.full(64, 1.0), np.full(64, 2.0)]).astype(np.float32)[None]
+    out, act = run_uniform(impl, uniform_problem(a=0.0, w13_byte=0, w2_byte=0), *IDENT, b13=b13,
+                           b2=np.ones((1, 128), np.float32))
+    assert np.max(np.abs(bf2f(act) - 2.0 / (1.0 + math.exp(-1.0)))) < 1e-2 and np.max(np.abs(out - 1.0)) < 1e-4
+    out, act = run_uniform(impl, uniform_problem(), *IDENT, swiglu_limit=10.0)
+    e10 = 10.0 / (1.0 + math.exp(-10.0)) * 10.0
+    assert np.max(np.abs(bf2f(act) - e10)) < 0.2 and np.max(np.abs(out - e10 * 64) / (e10 * 64)) < 1e-2
+    out, act = run_uniform(impl, uniform_problem(), *IDENT, swiglu_limit=1.0, activation=1, beta=4.0, linear_beta=25.0)
+    sig = 1.0 / (1.0 + math.exp(-128.0))
+    es = (4.0 * math.tanh(32.0) * sig) * (25.0 * math.tanh(128.0 / 25.0))
+    assert np.max(np.abs(bf2f(act) - es)) < 0.5 and np.max(np.abs(out - es * 64) / (es * 64)) < 1e-2
+    _, act = run_uniform(impl, uniform_problem(), *IDENT, swiglu_limit=1.0, activation=1, beta=4.0, linear_beta=0.0)
+    assert np.max(np.abs(bf2f(act) - 4.0 * math.tanh(32.0) * sig * 128.0)) < 0.5
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_decode_edges(impl):
+    """+-0.25 codes, inf/NaN codes, the 2^-127 scale, padding rows, dead blocks
+    (test_moe_fused.cpp:291-533)."""
+    out, act = run_uniform(impl, uniform_problem(w13_byte=0x11, w2_byte=0x11), *IDENT)
+    assert np.max(np.abs(bf2f(act) - 32.0 / (1.0 + math.exp(-32.0)) * 32.0)) < 0.5 and np.all(out > 0)
+    out, act = run_uniform(impl, uniform_problem(w13_byte=0x76, w2_byte=0x22), *IDENT)
+    assert np.all(np.isnan(bf2f(act))) and np.all(np.isnan(out))
+    out, act = run_uniform(impl, uniform_problem(w13_byte=0x22, w2_byte=0x22, scale=0), *IDENT)
+    assert np.max(np.abs(bf2f(act))) < 1e-30 and np.max(np.abs(out)) < 1e-30
+    sid = np.full(16, 8)
+    sid[:8] = np.arange(8)
+    out, act = run_uniform(impl, uniform_problem(M=8), sid, np.ones(16), np.zeros(1))
+    exp = 128.0 / (1.0 + math.exp(-128.0)) * 128.0 * 64
+    assert np.max(np.abs(out - exp) / exp) < 1e-2 and np.all(act[8:] == 0)
+    out, _ = run_uniform(impl, uniform_problem(), np.arange(16), np.ones(16), np.array([-1]), out_init=99.0)
+    assert np.all(out == 99.0)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_k3_routing_top16(impl):
+    """E = 256, top-16, one token: every 16-row block holds one real row (test_moe_fused.cpp:669-736)."""
+    E, top_k, hidden, ispp = 256, 16, 128, 64
+    prob = uniform_problem(M=1, hidden=hidden, ispp=ispp, E=E)
+    s, e, EM = oracle.moe_align_block_size(np.arange(top_k, dtype=np.int32)[None], E, 16)
+    out, act = run_uniform(impl, prob, s, oracle.gather_sorted_weights(np.ones(top_k, np.float32), s), e, top_k=top_k)
+    exp_act = hidden / (1.0 + math.exp(-hidden)) * hidden
+    real = s < top_k
+    assert np.max(np.abs(bf2f(act[real]) - exp_act)) < 0.5 and np.all(act[~real] == 0)
+    assert np.max(np.abs(out - top_k * exp_act * ispp) / (top_k * exp_act * ispp)) < 1e-2
+
+
+def _parity(cfg, T, *, impl, codes="finite", block_size=16, tokens=None, seed=None, logits=None, backend="numpy"):
+    w, A, r = make_case(cfg, T, codes=codes, seed=seed, backend=backend)
+    ids_np, tw_np, _ = oracle_route(cfg, A, r, logits=None if logits is None else to_np(logits))
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    got = to_np(gpu_layer(A, w, ids, tw, impl=impl, block_size=block_size, swiglu_limit=cfg.swiglu_limit))
+    ref = oracle_layer(A, w, ids, tw, tokens=tokens, swiglu_limit=cfg.swiglu_limit)
+    if tokens is not None:
+        got = got[tokens]
+    return assert_close_bf16(got, ref, f"{cfg.name} T={T} {impl}")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_c0_smoke_matches_oracle_and_golden(impl):
+    cfg = syn.CONFIGS["c0"]
+    _parity(cfg, 64, impl=impl)
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "c0_smoke.npz"))
+    w, A, _ = make_case(cfg, 64)
+    got = to_np(gpu_layer(A, w, torch.from_numpy(g["topk_ids"]).to(DEV), torch.from_numpy(g["topk_w"]).to(DEV), impl=impl))
+    assert_close_bf16(got, g["out"], "c0 vs golden (reference output)")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_c0_all_sixteen_codes_nan_mask(impl):
+    """With all 16 nibble codes a quarter of the weights are +-inf / NaN: the NaN mask of the
+    output must equal the oracle's (here: everything)."""
+    _parity(syn.CONFIGS["c0"], 64, impl=impl, codes="all")
+
+
+@pytest.mark.parametrize("T", [1, 8, 32, 64, 128])
+def test_c1_decode_sweep(T):
+    _parity(syn.CONFIGS["c1"], T, impl="tcgen05")
+
+
+def test_c1_golden_shape():
+    cfg = syn.scaled(syn.CONFIGS["c1"], E=4, top_k=2)
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "c1_shape_T8_E4.npz"))
+    w, A, _ = make_case(cfg, 8)
+    for impl in IMPLS:
+        got = to_np(gpu_layer(A, w, torch.from_numpy(g["topk_ids"]).to(DEV), torch.from_numpy(g["topk_w"]).to(DEV),
+                              impl=impl, swiglu_limit=cfg.swiglu_limit))
+        assert_close_bf16(got, g["out"], f"c1-shape golden {impl}")
+
+
+@pytest.mark.parametrize("block_size", [16, 64, 128])
+def test_block_sizes_and_bias(block_size):
+    cfg = syn.scaled(syn.CONFIGS["c0"], H=384, I=192, E=6, top_k=3)
+    w, A, r = make_case(cfg, 100)
+    ids_np, tw_np, _ = oracle_route(cfg, A, r)
+    rng = np.random.default_rng(1)
+    b13 = rng.standard_normal((cfg.E, 2 * cfg.I)).astype(np.float32)
+    b2 = rng.standard_normal((cfg.E, cfg.H)).astype(np.float32)
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    for impl in IMPLS:
+        for act_kw in (dict(swiglu_limit=0.7), dict(activation=1, beta=4.0, linear_beta=25.0)):
+            got = to_np(gpu_layer(A, w, ids, tw, impl=impl, block_size=block_size, b13=torch.from_numpy(b13).to(DEV),
+                                  b2=torch.from_numpy(b2).to(DEV), **act_kw))
+            ref = oracle_layer(A, w, ids, tw, b13=b13, b2=b2, **act_kw)
+            assert_close_bf16(got, ref, f"block {block_size} {impl} {act_kw}")
+
+
+def test_simt_accumulators_follow_the_oracle_order():
+    """The cross-check kernels add in the oracle's order: their act differs from the oracle's
+    only through the device expf, a few bf16 ulps on a handful of elements."""
+    cfg = syn.CONFIGS["c0"]
+    w, A, r = make_case(cfg, 64)
+    ids_np, tw_np, _ = oracle_route(cfg, A, r)
+    out, act, sids, eids, _ = gpu_layer(A, w, torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV),
+                                        impl="simt", return_parts=True)
+    s, e, EM = oracle.moe_align_block_size(ids_np, cfg.E, 16)
+    wn = {k: to_np(v) for k, v in w.items()}
+    st = oracle.moe_stages(bf16_to_u16(A), wn["w13"], wn["w13_scale"], wn["w2"], wn["w2_scale"], s,
+                           oracle.gather_sorted_weights(tw_np, s), e, top_k=cfg.top_k)
+    real = s < ids_np.size
+    ga, ra = bf16_to_u16(act)[:EM][real].astype(np.int32), st["act"][real].astype(np.int32)
+    assert (ga != ra).mean() < 0.01 and np.abs(ga - ra).max() <= 2
+    assert np.max(np.abs(to_np(out) - st["out"])) < 1e-4 * max(1.0, np.abs(st["out"]).max())
+
+
+@pytest.mark.parametrize("name,T,n_sub", [("c2", 8192, 192), ("c4", 4096, 128)])
+def test_prefill_shapes_on_a_token_subsample(name, T, n_sub):
+    """Full-size GPU run; the oracle evaluates a seeded subsample of the tokens, which equals
+    the full oracle run on those tokens (every row is independent)."""
+    cfg = syn.CONFIGS[name]
+    rng = np.random.default_rng(T)
+    tokens = np.sort(rng.choice(T, n_sub, replace=False))
+    logits = syn.make_zipf_logits(cfg, T, device=DEV) if cfg.zipf_alpha else None
+    _parity(cfg, T, impl="tcgen05", tokens=tokens, logits=logits, backend="torch")
+
+
+def test_c3_shape_with_shared_expert_on_a_token_subsample():
+    cfg = syn.CONFIGS["c3"]
+    T = 4096   # the full T = 16384 runs in bench.py; the weights (5.7 GB) are full size here
+    rng = np.random.default_rng(3)
+    tokens = np.sort(rng.choice(T, 64, replace=False))
+    _parity(cfg, T, impl="tcgen05", tokens=tokens, backend="torch")
+
+
+def test_full_size_properties_c2():
+    """Size-independent checks at the full prefill size: (1) doubling every routing weight doubles
+    the output (the combine is linear in the weights), (2) the tensor-core path and the
+    oracle-ordered CUDA-core path agree on every token, (3) permuting the tokens permutes the
+    output rows."""
+    cfg = syn.CONFIGS["c2"]
+    T = 8192
+    w, A, r = make_case(cfg, T, backend="torch")
+    lg = ops.router_logits(A, r["wr"])
+    ids, tw = ops.route_topk(lg, cfg.top_k)
+    ids, tw = ids.clone(), tw.clone()
+    base = gpu_layer(A, w, ids, tw, impl="tcgen05")
+    twice = gpu_layer(A, w, ids, tw * 2.0, impl="tcgen05")
+    assert_close_bf16(to_np(twice), 2.0 * to_np(base), "linearity in the routing weights")
+    simt = gpu_layer(A, w, ids, tw, impl="simt")
+    assert_close_bf16(to_np(base), to_np(simt), "tcgen05 vs oracle-ordered CUDA cores, all 8192 tokens")
+    perm = torch.randperm(T, device=DEV)
+    moved = gpu_layer(A[perm].contiguous(), w, ids[perm].contiguous(), tw[perm].contiguous(), impl="tcgen05")
+    assert_close_bf16(to_np(moved), to_np(base[perm]), "token permutation")
+
+
+def test_host_pointer_abi():
+    """vk_fused_moe_mxfp4 with HOST buffers (the CPU entry point's signature): copies in,
+    kernels, copies out; accumulates into `out` like the reference."""
+    cfg = syn.scaled(syn.CONFIGS["c0"], H=256, I=128, E=4, top_k=2)
+    w = {k: v.numpy() for k, v in syn.make_expert_weights(cfg).items()}
+    A = bf16_to_u16(syn.make_activations(cfg, 20))
+    r = syn.make_router(cfg)
+    ids, tw, _ = oracle.route_softmax_topk(oracle.router_logits(A, r["wr"].numpy()), cfg.top_k)
+    s, e, EM = oracle.moe_align_block_size(ids, cfg.E, 16)
+    ws = oracle.gather_sorted_weights(tw, s)
+    ref, _ = oracle.fused_moe_mxfp4(A, w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], s, ws, e, top_k=cfg.top_k)
+    out = np.full((20, cfg.H), 1.0, np.float32)
+    act = np.zeros((EM, cfg.I), np.uint16)
+    p = lambda a: a.ctypes.data
+    rc = nr.load_library().vk_fused_moe_mxfp4(p(A), p(w["w13"]), p(w["w13_scale"]), p(w["w2"]), p(w["w2_scale"]), p(s),
+                                              p(ws), p(e), p(act), p(out), 20, cfg.H, cfg.I, cfg.top_k, EM, 32, 0.0, 0,
+                                              4.0, 25.0, None, None)
+    assert rc == 0, nr.last_error()
+    assert_close_bf16(out - 1.0, ref, "host-pointer ABI")
+
+
+def test_layer_object_end_to_end():
+    """route -> align -> experts through the layer object, device and pinned-host entry."""
+    cfg = syn.CONFIGS["c0"]
+    w, A, r = make_case(cfg, 64)
+    layer = layer_from_config(cfg, w, r, max_tokens=128)
+    y = layer(A)
+    ids_np, tw_np, margin = oracle_route(cfg, A, r)
+    ref = oracle_layer(A, w, torch.from_numpy(ids_np), torch.from_numpy(tw_np))
+    ok = margin > 1e-4
+    assert_close_bf16(to_np(y.float())[ok], ref[ok], "layer object")
+    xh = A.cpu().pin_memory()
+    yh = torch.empty((64, cfg.H), dtype=torch.bfloat16).pin_memory()
+    layer.forward_host(xh, yh)
+    assert torch.equal(yh, y.cpu())

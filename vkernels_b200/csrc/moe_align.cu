@@ -1,0 +1,242 @@
+// moe_align.cu - device alignment of the routing table for any N = M*top_k.
+//
+// Output contract (reference moe_fused.cpp:609-661 for the order and padding,
+// moe_fused.hip:1983-2099 for expert_map / local_n / max_EM / out_em): flat
+// indices grouped by LOCAL expert in ascending order, ascending flat index
+// inside an expert (a stable counting sort), each expert padded to block_size
+// with the sentinel N, expert_ids = local expert per block and -1 beyond the
+// last real block, every one of the max_EM entries written, *out_em = padded
+// row count (block_size when nothing routes).
+//
+// Small N runs in one CTA (histogram, scan and scatter in shared memory).
+// Large N runs three kernels over 1024-entry chunks: per-chunk histograms,
+// a scan over (expert, chunk), and an ordered scatter; the chunk histograms
+// live in the library workspace.
+#include "common.cuh"
+#include "moe_fused.hpp"
+
+namespace vkernels::kernels::cuda {
+
+namespace {
+
+constexpr int kChunk = 1024;   // entries per chunk = threads per CTA
+constexpr int kWarps = kChunk / 32;
+
+__device__ __forceinline__ int local_expert(const int32_t* topk_ids, const int32_t* expert_map,
+                                            int i, int N, int num_experts, int local_n) {
+  if (i >= N) return -1;
+  int e = topk_ids[i];
+  if (e < 0 || e >= num_experts) return -1;
+  if (expert_map != nullptr) e = expert_map[e];
+  return (e < 0 || e >= local_n) ? -1 : e;
+}
+
+// Rank of each thread's entry among the chunk's entries with the same expert
+// (entries ordered by thread index), plus the chunk histogram in hist[0][*].
+//   warp_hist: [kWarps + 1][local_n] ints of shared memory.
+// On return warp_hist[w][e] = number of entries of expert e in warps < w and
+// warp_hist[kWarps][e] = the chunk total.
+__device__ __forceinline__ int chunk_rank(int le, int local_n, int* warp_hist) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < (kWarps + 1) * local_n; i += kChunk) warp_hist[i] = 0;
+  __syncthreads();
+  // peers = lanes of this warp holding the same expert (le = -1 groups too, ignored below)
+  const unsigned peers = __match_any_sync(0xFFFFFFFFu, le);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (le >= 0 && rank_in_warp == 0) warp_hist[warp * local_n + le] = __popc(peers);
+  __syncthreads();
+  // exclusive scan over warps, one thread per expert
+  for (int e = tid; e < local_n; e += kChunk) {
+    int run = 0;
+    for (int w = 0; w < kWarps; ++w) {
+      int c = warp_hist[w * local_n + e];
+      warp_hist[w * local_n + e] = run;
+      run += c;
+    }
+    warp_hist[kWarps * local_n + e] = run;
+  }
+  __syncthreads();
+  return le >= 0 ? warp_hist[warp * local_n + le] + rank_in_warp : 0;
+}
+
+// Exclusive scan of padded expert sizes by one CTA; writes expert_ids for the
+// real blocks, the row offset of every expert, and *out_em.
+//   count[e] : entries of expert e (shared or global)
+//   offset[e]: receives the first sorted row of expert e
+__device__ __forceinline__ void scan_experts(const int* count, int* offset, int local_n,
+                                             int block_size, int max_EM, int32_t* expert_ids,
+                                             int32_t* out_em, int* s_tmp /* [kChunk] */) {
+  const int tid = threadIdx.x;
+  // each thread owns a contiguous slice of experts
+  const int per = (local_n + kChunk - 1) / kChunk;
+  const int e0 = tid * per, e1 = min(local_n, e0 + per);
+  int mine = 0;
+  for (int e = e0; e < e1; ++e) mine += ((count[e] + block_size - 1) / block_size) * block_size;
+  s_tmp[tid] = mine;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over the 1024 per-thread sums
+  for (int d = 1; d < kChunk; d <<= 1) {
+    int v = (tid >= d) ? s_tmp[tid - d] : 0;
+    __syncthreads();
+    s_tmp[tid] += v;
+    __syncthreads();
+  }
+  int run = s_tmp[tid] - mine;
+  const int max_blocks = max_EM / block_size;
+  for (int e = e0; e < e1; ++e) {
+    offset[e] = run;
+    const int nb = (count[e] + block_size - 1) / block_size;
+    for (int b = 0; b < nb; ++b) {
+      const int blk = run / block_size + b;
+      if (blk < max_blocks) expert_ids[blk] = e;
+    }
+    run += nb * block_size;
+  }
+  if (tid == kChunk - 1) {
+    int EM = s_tmp[kChunk - 1];
+    if (EM == 0) EM = block_size;
+    if (EM > max_EM) EM = max_EM;
+    *out_em = EM;
+  }
+  __syncthreads();
+}
+
+// ------------------------------ one CTA, N <= kChunk -------------------------
+__global__ void __launch_bounds__(kChunk)
+align_small_kernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+                   int N, int block_size, int num_experts, int local_n, int max_EM,
+                   int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids,
+                   int32_t* __restrict__ out_em) {
+  extern __shared__ int smem[];
+  int* warp_hist = smem;                               // [(kWarps+1) * local_n]
+  int* offset = warp_hist + (kWarps + 1) * local_n;    // [local_n]
+  int* s_tmp = offset + local_n;                       // [kChunk]
+  const int tid = threadIdx.x;
+  for (int i = tid; i < max_EM; i += kChunk) sorted_ids[i] = N;
+  for (int i = tid; i < max_EM / block_size; i += kChunk) expert_ids[i] = -1;
+  const int le = local_expert(topk_ids, expert_map, tid, N, num_experts, local_n);
+  const int rank = chunk_rank(le, local_n, warp_hist);
+  scan_experts(warp_hist + kWarps * local_n, offset, local_n, block_size, max_EM, expert_ids,
+               out_em, s_tmp);
+  if (le >= 0) {
+    const int pos = offset[le] + rank;
+    if (pos < max_EM) sorted_ids[pos] = tid;
+  }
+}
+
+// ------------------------------ large N: three kernels -----------------------
+// 1) per-chunk histogram -> hist[chunk][e]; also fills the sentinels.
+__global__ void __launch_bounds__(kChunk)
+align_hist_kernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+                  int N, int block_size, int num_experts, int local_n, int max_EM,
+                  int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids,
+                  int* __restrict__ hist) {
+  extern __shared__ int smem[];
+  int* warp_hist = smem;
+  const int tid = threadIdx.x, chunk = blockIdx.x;
+  for (int i = chunk * kChunk + tid; i < max_EM; i += gridDim.x * kChunk) sorted_ids[i] = N;
+  for (int i = chunk * kChunk + tid; i < max_EM / block_size; i += gridDim.x * kChunk)
+    expert_ids[i] = -1;
+  const int le = local_expert(topk_ids, expert_map, chunk * kChunk + tid, N, num_experts, local_n);
+  (void)chunk_rank(le, local_n, warp_hist);
+  for (int e = tid; e < local_n; e += kChunk)
+    hist[(size_t)chunk * local_n + e] = warp_hist[kWarps * local_n + e];
+}
+
+// 2) one CTA: hist[chunk][e] -> exclusive over chunks (in place), totals ->
+//    expert offsets, expert_ids, out_em.
+__global__ void __launch_bounds__(kChunk)
+align_scan_kernel(int* __restrict__ hist, int n_chunks, int local_n, int block_size, int max_EM,
+                  int32_t* __restrict__ expert_ids, int32_t* __restrict__ out_em,
+                  int* __restrict__ offset /* [local_n] in workspace */) {
+  extern __shared__ int smem[];
+  int* count = smem;              // [local_n]
+  int* s_tmp = count + local_n;   // [kChunk]
+  const int tid = threadIdx.x;
+  for (int e = tid; e < local_n; e += kChunk) {
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      int v = hist[(size_t)c * local_n + e];
+      hist[(size_t)c * local_n + e] = run;
+      run += v;
+    }
+    count[e] = run;
+  }
+  __syncthreads();
+  scan_experts(count, offset, local_n, block_size, max_EM, expert_ids, out_em, s_tmp);
+}
+
+// 3) ordered scatter: row = expert offset + entries in earlier chunks + rank in chunk.
+__global__ void __launch_bounds__(kChunk)
+align_scatter_kernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+                     int N, int num_experts, int local_n, int max_EM,
+                     const int* __restrict__ hist, const int* __restrict__ offset,
+                     int32_t* __restrict__ sorted_ids) {
+  extern __shared__ int smem[];
+  int* warp_hist = smem;
+  const int tid = threadIdx.x, chunk = blockIdx.x;
+  const int i = chunk * kChunk + tid;
+  const int le = local_expert(topk_ids, expert_map, i, N, num_experts, local_n);
+  const int rank = chunk_rank(le, local_n, warp_hist);
+  if (le >= 0) {
+    const int pos = offset[le] + hist[(size_t)chunk * local_n + le] + rank;
+    if (pos < max_EM) sorted_ids[pos] = i;
+  }
+}
+
+}  // namespace
+
+void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, int M, int top_k,
+                          int block_size, int num_experts, int local_n, int max_EM,
+                          int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_em,
+                          void* stream) {
+  expects(block_size > 0, "moe_align_block_size: block_size must be positive");
+  expects(M >= 0 && top_k >= 0 && num_experts >= 0 && local_n >= 0,
+          "moe_align_block_size: negative dimension");
+  expects(max_EM > 0 && max_EM % block_size == 0,
+          "moe_align_block_size: max_EM must be a positive multiple of block_size");
+  expects(local_n <= num_experts, "moe_align_block_size: local_n exceeds num_experts");
+  expects(out_em != nullptr && sorted_ids != nullptr && expert_ids != nullptr,
+          "moe_align_block_size: output buffers must not be null");
+  expects(M == 0 || topk_ids != nullptr, "moe_align_block_size: topk_ids must not be null");
+  expects((long long)M * top_k < (1ll << 30), "moe_align_block_size: M*top_k too large");
+  const int N = M * top_k;
+  const int ln = local_n > 0 ? local_n : 1;  // shared-memory sizing only
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t hist_smem = (size_t)(kWarps + 1) * ln * sizeof(int);
+  expects(hist_smem + (size_t)(ln + kChunk) * sizeof(int) <= 200 * 1024,
+          "moe_align_block_size: too many local experts");
+  if (N <= kChunk) {
+    const size_t smem = hist_smem + (size_t)(ln + kChunk) * sizeof(int);
+    if (smem > 48 * 1024)
+      VK_CUDA_CHECK(cudaFuncSetAttribute(align_small_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    align_small_kernel<<<1, kChunk, smem, s>>>(topk_ids, expert_map, N, block_size, num_experts,
+                                               local_n, max_EM, sorted_ids, expert_ids, out_em);
+  } else {
+    const int n_chunks = (N + kChunk - 1) / kChunk;
+    int* ws = static_cast<int*>(workspace_get(((size_t)n_chunks * ln + ln) * sizeof(int)));
+    int* hist = ws;
+    int* offset = ws + (size_t)n_chunks * ln;
+    if (hist_smem > 48 * 1024) {
+      VK_CUDA_CHECK(cudaFuncSetAttribute(align_hist_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)hist_smem));
+      VK_CUDA_CHECK(cudaFuncSetAttribute(align_scatter_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)hist_smem));
+    }
+    align_hist_kernel<<<n_chunks, kChunk, hist_smem, s>>>(topk_ids, expert_map, N, block_size,
+                                                          num_experts, local_n, max_EM, sorted_ids,
+                                                          expert_ids, hist);
+    const size_t scan_smem = (size_t)(ln + kChunk) * sizeof(int);
+    align_scan_kernel<<<1, kChunk, scan_smem, s>>>(hist, n_chunks, local_n, block_size, max_EM,
+                                                   expert_ids, out_em, offset);
+    align_scatter_kernel<<<n_chunks, kChunk, hist_smem, s>>>(topk_ids, expert_map, N, num_experts,
+                                                             local_n, max_EM, hist, offset,
+                                                             sorted_ids);
+  }
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace vkernels::kernels::cuda

@@ -1,0 +1,148 @@
+// moe_fused.cu - host launchers: argument contract, workspace, dispatch.
+#include "moe_fused.hpp"
+
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace vkernels::kernels::cuda {
+
+// defined in moe_simt.cu / moe_gemm_sm100.cu
+void launch_moe_simt(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                     const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w, int w_sorted,
+                     uint16_t* act_scratch, float* out, int M, int hidden, int ispp, int top_k,
+                     const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                     float swiglu_limit, int activation, float beta, float linear_beta,
+                     const float* b13, const float* b2, int block_size, cudaStream_t stream);
+void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                      const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                      int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
+                      int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                      float swiglu_limit, int activation, float beta, float linear_beta,
+                      const float* b13, const float* b2, int block_size, cudaStream_t stream);
+size_t sm100_workspace_bytes(int EM, int hidden, int ispp);
+
+// ---------------------------------------------------------------------------
+// implementation switch
+// ---------------------------------------------------------------------------
+namespace {
+std::atomic<int> g_impl{-1};
+int impl_from_env() {
+  const char* s = std::getenv("VK_MOE_IMPL");
+  if (s != nullptr && std::strcmp(s, "simt") == 0) return (int)MoeImpl::kSimt;
+  return (int)MoeImpl::kTcgen05;
+}
+}  // namespace
+
+void set_moe_impl(MoeImpl impl) { g_impl.store((int)impl); }
+MoeImpl get_moe_impl() {
+  int v = g_impl.load();
+  if (v < 0) {
+    v = impl_from_env();
+    g_impl.store(v);
+  }
+  return (MoeImpl)v;
+}
+
+// ---------------------------------------------------------------------------
+// workspace: one grow-only block per device
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kMaxDevices = 64;
+Workspace g_ws[kMaxDevices];
+std::mutex g_ws_mutex;
+}  // namespace
+
+void* workspace_get(size_t bytes) {
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  expects(dev >= 0 && dev < kMaxDevices, "workspace: device index out of range");
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  Workspace& ws = g_ws[dev];
+  if (ws.bytes < bytes) {
+    // Work already enqueued may still read the old block.
+    VK_CUDA_CHECK(cudaDeviceSynchronize());
+    if (ws.ptr != nullptr) VK_CUDA_CHECK(cudaFree(ws.ptr));
+    ws.ptr = nullptr;
+    ws.bytes = 0;
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    VK_CUDA_CHECK(cudaMalloc(&ws.ptr, want));
+    // the first 4 KB hold counters and the status word of the GEMM kernels
+    VK_CUDA_CHECK(cudaMemset(ws.ptr, 0, 4096));
+    ws.bytes = want;
+  }
+  return ws.ptr;
+}
+
+void reserve_workspace(size_t bytes) { (void)workspace_get(bytes); }
+
+size_t workspace_bytes_required(int max_EM, int hidden, int ispp, int n_local_experts, int N) {
+  const size_t align_bytes =
+      ((size_t)((N + 1023) / 1024) + 1) * (size_t)(n_local_experts > 0 ? n_local_experts : 1) * 4;
+  const size_t gemm_bytes = sm100_workspace_bytes(max_EM, hidden, ispp);
+  return (align_bytes > gemm_bytes ? align_bytes : gemm_bytes) + 4096;
+}
+
+// ---------------------------------------------------------------------------
+// fused layer
+// ---------------------------------------------------------------------------
+namespace {
+void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+               const uint8_t* w2_scale, const float* topk_w, int w_sorted, uint16_t* act_scratch,
+               float* out, int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+               const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
+               float linear_beta, const float* b13, const float* b2, int block_size, bool kmajor,
+               void* stream) {
+  expects(!kmajor, "fused_moe_mxfp4: the K-major weight layout is not supported");
+  expects(M >= 0 && EM >= 0 && top_k > 0, "fused_moe_mxfp4: bad M / EM / top_k");
+  expects(hidden > 0 && hidden % 64 == 0, "fused_moe_mxfp4: hidden must be a multiple of 64");
+  expects(ispp > 0 && ispp % 64 == 0, "fused_moe_mxfp4: ispp must be a multiple of 64");
+  expects(block_size >= 16 && block_size % 16 == 0,
+          "fused_moe_mxfp4: block_size must be a multiple of 16");
+  expects(EM % block_size == 0, "fused_moe_mxfp4: EM must be a multiple of block_size");
+  expects(activation == kSwiGLU || activation == kSiTU, "fused_moe_mxfp4: unknown activation");
+  expects((long long)M * top_k < (1ll << 30), "fused_moe_mxfp4: M*top_k too large");
+  if (M == 0 || EM == 0) return;
+  expects(A && w13 && w13_scale && w2 && w2_scale && topk_w && act_scratch && out &&
+              sorted_ids && expert_ids,
+          "fused_moe_mxfp4: buffers must not be null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (get_moe_impl() == MoeImpl::kSimt)
+    launch_moe_simt(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M, hidden,
+                    ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta,
+                    linear_beta, b13, b2, block_size, s);
+  else
+    launch_moe_sm100(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M,
+                     hidden, ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation,
+                     beta, linear_beta, b13, b2, block_size, s);
+}
+}  // namespace
+
+void fused_moe_mxfp4(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                     const uint8_t* w2, const uint8_t* w2_scale, const int32_t* /*topk_ids*/,
+                     const float* topk_w, uint16_t* act_scratch, float* out, int M, int hidden,
+                     int ispp, int top_k, const int32_t* sorted_ids, const int32_t* expert_ids,
+                     int EM, float swiglu_limit, int activation, float beta, float linear_beta,
+                     const float* b13, const float* b2, int block_size, bool kmajor,
+                     void* stream) {
+  run_fused(A, w13, w13_scale, w2, w2_scale, topk_w, 0, act_scratch, out, M, hidden, ispp, top_k,
+            sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2,
+            block_size, kmajor, stream);
+}
+
+void fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                              const uint8_t* w2, const uint8_t* w2_scale,
+                              const float* topk_w_sorted, uint16_t* act_scratch, float* out,
+                              int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                              const int32_t* expert_ids, int EM, float swiglu_limit,
+                              int activation, float beta, float linear_beta, const float* b13,
+                              const float* b2, int block_size, void* stream) {
+  run_fused(A, w13, w13_scale, w2, w2_scale, topk_w_sorted, 1, act_scratch, out, M, hidden, ispp,
+            top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13,
+            b2, block_size, false, stream);
+}
+
+}  // namespace vkernels::kernels::cuda

@@ -1,0 +1,95 @@
+// moe_fused.hpp - C++ launcher interface of the B200 fused MXFP4 MoE layer.
+//
+// The two launchers keep the argument lists of the reference's device entry
+// points (src/c/vkernels/kernels/moe_fused.hpp:322-344 `fused_moe_mxfp4`,
+// :382-390 `moe_align_block_size_hip`) so a caller of those compiles against
+// this header by switching the namespace. Everything else here is additive.
+//
+// All pointers are device pointers unless a name ends in `_host`. Launchers
+// enqueue on `stream` and return; they never synchronise.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace vkernels::kernels {
+
+// Epilogue tag (reference moe_fused.hpp:47-50).
+enum MoEActivation : int { kSwiGLU = 0, kSiTU = 1 };
+
+namespace cuda {
+
+// Which device implementation runs the two grouped GEMMs.
+//   kTcgen05 : persistent tcgen05/TMEM kernels (default)
+//   kSimt    : one-thread-per-output CUDA-core kernels that add in the CPU
+//              oracle's order; a slow cross-check, selected only explicitly
+//              (env VK_MOE_IMPL=simt or set_moe_impl), never as a fallback.
+enum class MoeImpl : int { kTcgen05 = 0, kSimt = 1 };
+void set_moe_impl(MoeImpl impl);
+MoeImpl get_moe_impl();
+
+// Fused layer: act = epilogue(gather(A) @ w13^T + b13); out += w * (act @ w2^T + b2).
+//   A [M, hidden] bf16; w13 [E, 2*ispp, hidden/2] packed E2M1 (gate rows then up
+//   rows); w13_scale [E, 2*ispp, hidden/32] ue8m0; w2 [E, hidden, ispp/2];
+//   w2_scale [E, hidden, ispp/32]; topk_w [M*top_k] raw routing weights read at
+//   the flat index; act_scratch [EM, ispp] bf16 (padding rows never written);
+//   out [M, hidden] fp32, accumulated into (the caller zeroes it);
+//   sorted_ids [EM] / expert_ids [EM/block_size] from the alignment below.
+// block_size is the alignment granularity of expert_ids (16, 64 or 128).
+// kmajor is accepted for signature compatibility and must be false.
+// Throws std::invalid_argument on a contract violation, std::runtime_error on
+// a CUDA failure.
+void fused_moe_mxfp4(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                     const uint8_t* w2, const uint8_t* w2_scale, const int32_t* topk_ids,
+                     const float* topk_w, uint16_t* act_scratch, float* out, int M, int hidden,
+                     int ispp, int top_k, const int32_t* sorted_ids, const int32_t* expert_ids,
+                     int EM, float swiglu_limit, int activation = kSwiGLU, float beta = 4.0f,
+                     float linear_beta = 25.0f, const float* b13 = nullptr,
+                     const float* b2 = nullptr, int block_size = 16, bool kmajor = false,
+                     void* stream = nullptr);
+
+// Same layer, routing weights already gathered into sorted-row order
+// (`topk_w_sorted [EM]`, the CPU entry point's convention, reference
+// moe_fused.hpp:83-101).
+void fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                              const uint8_t* w2, const uint8_t* w2_scale,
+                              const float* topk_w_sorted, uint16_t* act_scratch, float* out,
+                              int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                              const int32_t* expert_ids, int EM, float swiglu_limit,
+                              int activation, float beta, float linear_beta, const float* b13,
+                              const float* b2, int block_size, void* stream);
+
+// Device alignment, any N = M*top_k (the reference stops at 1024). Output is
+// bit-identical to the host `moe_align_block_size`: experts ascending, flat
+// index ascending inside an expert, each expert padded to block_size with N,
+// expert_ids -1 beyond the last real block; all max_EM entries are written;
+// *out_em receives the real EM (block_size when nothing routes).
+void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, int M, int top_k,
+                          int block_size, int num_experts, int local_n, int max_EM,
+                          int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_em,
+                          void* stream = nullptr);
+
+// logits[t, e] = sum_k fp32(x[t, k]) * wr[e, k]   (x bf16 [T, H], wr fp32 [E, H]).
+void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H, int E,
+                   void* stream);
+
+// Softmax top-k (reference torch_ops/tokenspeed_amd/routing.py:58-145) or, with
+// sigmoid != 0, sigmoid + bias with optional group limiting
+// (torch_ops/glm_router.py:184-201 plus group selection by the sum of the two
+// largest biased scores). ids/w are [T, k + n_shared]; the n_shared trailing
+// slots carry expert ids E, E+1, .. with weight 1 (glm_router.py:253-262).
+void route_topk(const float* logits, const float* bias, int T, int E, int k, int sigmoid,
+                int n_group, int topk_group, int renorm, float scaling, int n_shared,
+                int32_t* ids, float* w, void* stream);
+
+// Library-owned device scratch (tile lists, alignment histograms, the gathered
+// activation rows of the gate/up GEMM). It is sized on first use and grown
+// when a larger problem arrives; growth calls cudaMalloc and therefore must
+// not happen during stream capture: call reserve_workspace once, before
+// capture, with the largest problem.
+size_t workspace_bytes_required(int max_EM, int hidden, int ispp, int n_local_experts,
+                                int N);
+void reserve_workspace(size_t bytes);
+
+}  // namespace cuda
+}  // namespace vkernels::kernels

@@ -1,0 +1,882 @@
+// moe_gemm_sm100.cu - the two grouped GEMMs of the fused MXFP4 MoE layer on
+// tcgen05 tensor cores (sm_100a only).
+//
+// Orientation: the WEIGHTS are the M operand. One work item is 128 weight rows
+// (gate/up GEMM: 64 gate rows + the 64 matching up rows; down GEMM: 128 rows)
+// against up to 256 tokens of ONE expert. A thread of a dequant warp owns one
+// weight row = one TMEM lane: it reads the row's packed nibbles (K-contiguous,
+// exactly the memory layout of the weights), expands them to bf16 with the
+// exact table (common.cuh) and stores them with tcgen05.st as the A operand in
+// tensor memory; the scale of a 32-element group is a per-thread scalar. The
+// tokens are the N operand (any multiple of 16 up to 256), staged in shared
+// memory by TMA with the 128-byte swizzle, so a ragged expert costs at most 15
+// padded columns and a decode batch with a handful of tokens per expert still
+// fills all 128 tensor-core rows. Accumulators D[weight row, token] stay in
+// tensor memory (fp32) until the epilogue:
+//   gate/up : bias, activation, ONE rounding to bf16, act[row, feature] store
+//   down    : bias, routing weight, red.global.add.f32 into out[token, h]
+//             (the weighted un-permute/combine, fused)
+//
+// Warp roles (512 threads, one persistent CTA per SM):
+//   warp 0      TMA producer: packed weights (2 boxes of 64 rows x 128 B per
+//               256-K stage), scale bytes (bulk copy per item), token tiles
+//   warp 1      tcgen05.mma issuer + tensor-memory allocation
+//   warps 4-11  dequant: shared memory -> registers -> tensor memory
+//   warps 12-15 epilogue: tensor memory -> registers -> global
+// Tensor memory (512 columns): 0..255 accumulator, 256..511 eight A stages of
+// 64 K-elements (32 columns each).
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises a flag all
+// roles observe, the CTA frees its tensor memory and returns, and the launcher
+// reports the failure through the device-side status word.
+//
+// Reference behaviour replaced: gateup_swiglu_kernel* and down_combine_kernel*
+// (src/c/vkernels/kernels/moe_fused.hip:681-1436) and their launcher
+// (moe_fused.hip:1448-1663).
+#include <cuda.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "moe_fused.hpp"
+
+namespace vkernels::kernels::cuda {
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// geometry
+// ---------------------------------------------------------------------------
+constexpr int kMaxTok = 256;        // tokens (MMA N) per work item
+constexpr int kRows = 128;          // weight rows (MMA M) per work item
+constexpr int kWStageK = 256;       // K elements per packed-weight stage (128 B per row)
+constexpr int kSubK = 64;           // K elements per A stage / token stage (128 B of bf16)
+constexpr int kWStages = 3;
+constexpr int kAStages = 8;
+constexpr int kWStageBytes = kRows * 128;          // 16 KB
+constexpr int kBStageBytes = kMaxTok * 128;        // 32 KB
+constexpr int kStageRowPad = 129;                  // fp32 row pitch of the epilogue staging
+constexpr int kEpiStageBytes = 32 * kStageRowPad * 4;
+constexpr int kThreads = 512;
+constexpr int kAccCols = 256;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kSpinLimit = 40u * 1000u * 1000u;
+
+struct TokTile {
+  int expert;
+  int row0;
+  int n_rows;  // multiple of 16, <= kMaxTok
+  int pad;
+};
+
+struct GemmParams {
+  const uint8_t* w_scale;     // [E, n_wrows, K/32]
+  const float* bias;          // gate/up: [E, 2*n_feat]; down: [E, n_feat]; or null
+  const float* topk_w;        // down only
+  const int32_t* sorted_ids;  // [EM]
+  uint16_t* act;              // gate/up output [EM, n_feat]
+  float* out;                 // down output [M, n_feat]
+  const TokTile* tiles;
+  const int* n_tiles;
+  int* status;                // device status word (0 = ok)
+  int K;                      // reduction length (hidden for gate/up, ispp for down)
+  int n_feat;                 // gate/up: ispp; down: hidden
+  int n_ftiles;
+  int N;                      // M * top_k (sentinel of padded rows)
+  int top_k;
+  int w_sorted;
+  int b_stages;
+  int scale_bufs;
+  int scale_buf_bytes;
+  int activation;
+  float limit, beta, linear_beta;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the CTA is aborting (this wait or another
+// role's ran out of iterations).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      if (it > kSpinLimit) {
+        *abort_flag = code;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]; kind::f16 with bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are
+// 128 bytes (64 bf16) with the 128-byte swizzle: groups of 8 rows are 1024
+// bytes apart (stride byte offset), version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // descriptor version
+  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// shared-memory carve-up
+// ---------------------------------------------------------------------------
+struct Barriers {
+  uint64_t w_full[kWStages], w_empty[kWStages];
+  uint64_t a_full[kAStages], a_empty[kAStages];
+  uint64_t b_full[8], b_empty[8];
+  uint64_t sc_full[2], sc_empty[2];
+  uint64_t acc_full, acc_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+  int tile_tok[kMaxTok];
+  float tile_w[kMaxTok];
+};
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <bool GATEUP>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* w_smem = smem;                                      // kWStages x 16 KB
+  uint8_t* b_smem = w_smem + kWStages * kWStageBytes;          // b_stages x 32 KB
+  uint8_t* sc_smem = b_smem + p.b_stages * kBStageBytes;       // scale_bufs x scale_buf_bytes
+  float* epi_stage = reinterpret_cast<float*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
+  Barriers* bars = reinterpret_cast<Barriers*>(reinterpret_cast<uint8_t*>(epi_stage) +
+                                               (GATEUP ? kEpiStageBytes : 0));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (tid == 0) {
+    for (int i = 0; i < kWStages; ++i) {
+      mbar_init(smem_u32(&bars->w_full[i]), 1);
+      mbar_init(smem_u32(&bars->w_empty[i]), 8);
+    }
+    for (int i = 0; i < kAStages; ++i) {
+      mbar_init(smem_u32(&bars->a_full[i]), 8);
+      mbar_init(smem_u32(&bars->a_empty[i]), 1);
+    }
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(smem_u32(&bars->b_full[i]), 1);
+      mbar_init(smem_u32(&bars->b_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->sc_full[i]), 1);
+      mbar_init(smem_u32(&bars->sc_empty[i]), 8);
+    }
+    mbar_init(smem_u32(&bars->acc_full), 1);
+    mbar_init(smem_u32(&bars->acc_empty), 4);
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int n_tok_tiles = *p.n_tiles;
+  const int n_items = n_tok_tiles * p.n_ftiles;
+  const int n_kw = (p.K + kWStageK - 1) / kWStageK;   // packed-weight stages per item
+  const int n_sub_total = p.K / kSubK;                // A / token stages per item
+  const int pitch = p.K / 32;                         // scale bytes per weight row
+  const int n_wrows = GATEUP ? 2 * p.n_feat : p.n_feat;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ---------------------------
+    if (lane == 0) {
+      uint32_t w_it = 0, b_it = 0, sc_it = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const TokTile tt = p.tiles[item / p.n_ftiles];
+        const int f = item % p.n_ftiles;
+        // weight rows of this item: two boxes of 64 rows
+        int row_a, row_b, rows_valid;
+        if (GATEUP) {
+          row_a = tt.expert * n_wrows + f * 64;
+          row_b = row_a + p.n_feat;
+          rows_valid = 128;
+        } else {
+          row_a = tt.expert * n_wrows + f * 128;
+          row_b = row_a + 64;
+          rows_valid = min(128, p.n_feat - f * 128);
+        }
+        // scales of the item's rows
+        {
+          const int sb = sc_it % p.scale_bufs;
+          const uint32_t par = ((sc_it / p.scale_bufs) & 1u) ^ 1u;
+          if (!mbar_wait(smem_u32(&bars->sc_empty[sb]), par, abort_flag, 1)) break;
+          const uint32_t bar = smem_u32(&bars->sc_full[sb]);
+          const uint32_t dst = smem_u32(sc_smem + sb * p.scale_buf_bytes);
+          const uint32_t half = 64u * pitch;
+          mbar_expect_tx(bar, rows_valid == 128 ? 2 * half : half);
+          bulk_load_1d(dst, p.w_scale + (size_t)row_a * pitch, half, bar);
+          if (rows_valid == 128)
+            bulk_load_1d(dst + half, p.w_scale + (size_t)row_b * pitch, half, bar);
+          ++sc_it;
+        }
+        int sub = 0;
+        bool ok = true;
+        for (int kw = 0; kw < n_kw && ok; ++kw) {
+          {
+            const int s = w_it % kWStages;
+            const uint32_t par = ((w_it / kWStages) & 1u) ^ 1u;
+            if (!mbar_wait(smem_u32(&bars->w_empty[s]), par, abort_flag, 2)) { ok = false; break; }
+            const uint32_t bar = smem_u32(&bars->w_full[s]);
+            const uint32_t dst = smem_u32(w_smem + s * kWStageBytes);
+            mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
+            tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
+            if (rows_valid == 128) tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
+            ++w_it;
+          }
+          const int n_sub = min(4, n_sub_total - kw * 4);
+          for (int j = 0; j < n_sub; ++j, ++sub) {
+            const int s = b_it % p.b_stages;
+            const uint32_t par = ((b_it / p.b_stages) & 1u) ^ 1u;
+            if (!mbar_wait(smem_u32(&bars->b_empty[s]), par, abort_flag, 3)) { ok = false; break; }
+            const uint32_t bar = smem_u32(&bars->b_full[s]);
+            const uint32_t dst = smem_u32(b_smem + s * kBStageBytes);
+            mbar_expect_tx(bar, tt.n_rows * 128);
+            for (int r = 0; r < tt.n_rows; r += 16)
+              tma_load_2d(dst + r * 128, &tmap_b, sub * kSubK, tt.row0 + r, bar);
+            ++b_it;
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer -----------------------------
+    if (lane == 0) {
+      uint32_t a_it = 0, b_it = 0, item_it = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
+        const TokTile tt = p.tiles[item / p.n_ftiles];
+        const uint32_t idesc = make_idesc(tt.n_rows);
+        if (!mbar_wait(smem_u32(&bars->acc_empty), (item_it & 1u) ^ 1u, abort_flag, 4)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int sub = 0; sub < n_sub_total; ++sub) {
+          const int sa = a_it % kAStages, sb = b_it % p.b_stages;
+          if (!mbar_wait(smem_u32(&bars->a_full[sa]), (a_it / kAStages) & 1u, abort_flag, 5) ||
+              !mbar_wait(smem_u32(&bars->b_full[sb]), (b_it / p.b_stages) & 1u, abort_flag, 6)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t b_addr = smem_u32(b_smem + sb * kBStageBytes);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            tc_mma_ts(tmem_base, tmem_base + kAccCols + sa * 32 + kk * 8,
+                      make_b_desc(b_addr + kk * 32), idesc, (sub | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bars->a_empty[sa]));
+          tc_commit(smem_u32(&bars->b_empty[sb]));
+          ++a_it;
+          ++b_it;
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bars->acc_full));
+      }
+    }
+  } else if (warp >= 4 && warp < 12) {
+    // ------------------------------ dequant --------------------------------
+    const int q = warp & 3, h = (warp - 4) >> 2;   // TMEM lane quarter, K half of a 64-K stage
+    const int row = q * 32 + lane;                 // weight row inside the item
+    uint32_t w_it = 0, a_it = 0, sc_it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int f = item % p.n_ftiles;
+      const int rows_valid = GATEUP ? 128 : min(128, p.n_feat - f * 128);
+      const int sbuf = sc_it % p.scale_bufs;
+      if (!mbar_wait(smem_u32(&bars->sc_full[sbuf]), (sc_it / p.scale_bufs) & 1u, abort_flag, 7)) {
+        ok = false;
+        break;
+      }
+      const uint8_t* my_scales = sc_smem + sbuf * p.scale_buf_bytes + row * pitch;
+      for (int kw = 0; kw < n_kw && ok; ++kw) {
+        const int sw = w_it % kWStages;
+        if (!mbar_wait(smem_u32(&bars->w_full[sw]), (w_it / kWStages) & 1u, abort_flag, 8)) {
+          ok = false;
+          break;
+        }
+        const uint8_t* my_row = w_smem + sw * kWStageBytes + (row >> 6) * (kWStageBytes / 2) +
+                                (row & 63) * 128;
+        const int n_sub = min(4, n_sub_total - kw * 4);
+        for (int j = 0; j < n_sub; ++j) {
+          const int sa = a_it % kAStages;
+          if (!mbar_wait(smem_u32(&bars->a_empty[sa]), ((a_it / kAStages) & 1u) ^ 1u, abort_flag,
+                         9)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t v[16];
+          if (row < rows_valid) {
+            const int chunk = j * 2 + h;  // 16-byte chunk = 32 K elements = one scale group
+            const uint4 pk = *reinterpret_cast<const uint4*>(my_row + ((chunk ^ (row & 7)) << 4));
+            const uint32_t sc2 = ue8m0_to_bf16x2(my_scales[kw * 8 + chunk]);
+            dequant8(pk.x, sc2, v + 0);
+            dequant8(pk.y, sc2, v + 4);
+            dequant8(pk.z, sc2, v + 8);
+            dequant8(pk.w, sc2, v + 12);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0u;
+          }
+          tc_st16(tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols + sa * 32 + h * 16, v);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[sa]));
+          ++a_it;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->w_empty[sw]));
+        ++w_it;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->sc_empty[sbuf]));
+      ++sc_it;
+    }
+  } else if (warp >= 12) {
+    // ------------------------------ epilogue -------------------------------
+    const int q = warp & 3;
+    const int etid = tid - 12 * 32;  // 0..127 = TMEM lane
+    uint32_t item_it = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
+      const TokTile tt = p.tiles[item / p.n_ftiles];
+      const int f = item % p.n_ftiles;
+      // per-token info of this item (previous item's readers are past the barrier below)
+      named_bar_sync(1, 128);
+      for (int j = etid; j < tt.n_rows; j += 128) {
+        const int flat = p.sorted_ids[tt.row0 + j];
+        const bool real = flat >= 0 && flat < p.N;
+        bars->tile_tok[j] = real ? (GATEUP ? 1 : flat / p.top_k) : -1;
+        if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
+      }
+      named_bar_sync(1, 128);
+      if (!mbar_wait(smem_u32(&bars->acc_full), item_it & 1u, abort_flag, 10)) break;
+      tc_fence_after();
+      const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+      if (GATEUP) {
+        const int tok = lane, fq = q;  // second phase: token = lane, 16 features per warp
+        float bg[16], bu[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          bg[j] = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + f * 64 + fq * 16 + j] : 0.0f;
+          bu[j] = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + p.n_feat + f * 64 + fq * 16 + j]
+                         : 0.0f;
+        }
+        for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+          uint32_t v[32];
+          tc_ld32(t_lane + c0, v);
+          tc_wait_ld();
+          if (c0 + 32 >= tt.n_rows) {  // last read of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) epi_stage[j * kStageRowPad + etid] = __uint_as_float(v[j]);
+          named_bar_sync(2, 128);
+          const int t = c0 + tok;
+          if (t < tt.n_rows && bars->tile_tok[t] >= 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float r[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const float g = epi_stage[tok * kStageRowPad + fq * 16 + j + u] + bg[j + u];
+                const float up = epi_stage[tok * kStageRowPad + 64 + fq * 16 + j + u] + bu[j + u];
+                r[u] = moe_act_value(p.activation, g, up, p.limit, p.beta, p.linear_beta);
+              }
+              packed[j >> 1] = (uint32_t)f32_to_bf16_bits(r[0]) | ((uint32_t)f32_to_bf16_bits(r[1]) << 16);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(p.act + (size_t)(tt.row0 + t) * p.n_feat + f * 64 +
+                                                  fq * 16);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          }
+          named_bar_sync(2, 128);
+        }
+      } else {
+        const int rows_valid = min(128, p.n_feat - f * 128);
+        const int h = f * 128 + etid;
+        const bool row_ok = etid < rows_valid;
+        const float b = (p.bias && row_ok) ? p.bias[(size_t)tt.expert * p.n_feat + h] : 0.0f;
+        for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+          uint32_t v[32];
+          tc_ld32(t_lane + c0, v);
+          tc_wait_ld();
+          if (c0 + 32 >= tt.n_rows) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int t = c0 + j;
+              if (t < tt.n_rows) {
+                const int token = bars->tile_tok[t];
+                if (token >= 0) {
+                  const float val = (__uint_as_float(v[j]) + b) * bars->tile_w[t];
+                  atomicAdd(p.out + (size_t)token * p.n_feat + h, val);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ---------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+  if (tid == 0 && bars->abort_flag != 0) atomicExch(p.status, 100 + bars->abort_flag);
+}
+
+// ---------------------------------------------------------------------------
+// pre-pass kernels
+// ---------------------------------------------------------------------------
+
+// Token tiles from expert_ids: a run of consecutive blocks with the same
+// non-negative expert becomes ceil(rows / kMaxTok) tiles of (almost) equal
+// size, each a multiple of 16 rows.
+__global__ void __launch_bounds__(1024)
+build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size,
+                   TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+  __shared__ int scan[1024];
+  __shared__ int base;
+  const int tid = threadIdx.x;
+  if (tid == 0) base = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < n_blocks; b0 += 1024) {
+    const int b = b0 + tid;
+    int e = -1, run_blocks = 0;
+    if (b < n_blocks) {
+      e = expert_ids[b];
+      const bool start = e >= 0 && (b == 0 || expert_ids[b - 1] != e);
+      if (start) {
+        run_blocks = 1;
+        while (b + run_blocks < n_blocks && expert_ids[b + run_blocks] == e) ++run_blocks;
+      }
+    }
+    const int rows = run_blocks * block_size;
+    const int nt = (rows + kMaxTok - 1) / kMaxTok;
+    scan[tid] = nt;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {
+      const int v = tid >= d ? scan[tid - d] : 0;
+      __syncthreads();
+      scan[tid] += v;
+      __syncthreads();
+    }
+    if (nt > 0) {
+      int at = base + scan[tid] - nt;
+      // equal split, rounded up to 16 rows
+      const int per = (((rows + nt - 1) / nt) + 15) & ~15;
+      int r = 0;
+      for (int i = 0; i < nt; ++i, ++at) {
+        const int n = min(per, rows - r);
+        if (at < max_tiles && n > 0) tiles[at] = TokTile{e, b * block_size + r, n, 0};
+        r += n;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) base += scan[1023];
+    __syncthreads();
+  }
+  if (tid == 0) *n_tiles = min(base, max_tiles);
+}
+
+// A_sorted[r, :] = A[sorted_ids[r] / top_k, :] for real rows, zeros otherwise.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint16_t* __restrict__ A, const int32_t* __restrict__ sorted_ids,
+                   const int32_t* __restrict__ expert_ids, int block_size, int EM, int N, int top_k,
+                   int H, uint16_t* __restrict__ dst) {
+  const int vec_per_row = H / 8;  // 16-byte vectors
+  const int rows_per_cta = 4;
+  const int r0 = blockIdx.x * rows_per_cta;
+  for (int rr = 0; rr < rows_per_cta; ++rr) {
+    const int r = r0 + rr;
+    if (r >= EM) return;
+    if (expert_ids[r / block_size] < 0) continue;  // never read by any tile
+    const int flat = sorted_ids[r];
+    const bool real = flat >= 0 && flat < N;
+    const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)(real ? flat / top_k : 0) * H);
+    uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * H);
+    for (int i = threadIdx.x; i < vec_per_row; i += 256)
+      d[i] = real ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps, workspace layout, launch
+// ---------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    VK_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+    if (p == nullptr || qres != cudaDriverEntryPointSuccess)
+      throw std::runtime_error("cuTensorMapEncodeTiled is not available from the driver");
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t inner, outer, pitch;
+  uint32_t box_inner, box_outer;
+  int dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && pitch == o.pitch &&
+           box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype;
+  }
+};
+
+// Row-major 2-D tensor [outer, inner] with a byte pitch; box = [box_outer, box_inner];
+// 128-byte swizzle. Encoded maps are cached: encoding costs a few microseconds
+// and a decode step has only ~10 us in total.
+CUtensorMap make_map(const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,
+                     uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  static std::mutex mu;
+  static std::vector<std::pair<MapKey, CUtensorMap>> cache;
+  const MapKey key{ptr, inner, outer, pitch_bytes, box_inner, box_outer, (int)dt};
+  std::lock_guard<std::mutex> lock(mu);
+  for (auto& kv : cache)
+    if (kv.first == key) return kv.second;
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  expects(box_inner * elem_bytes == 128, "tensor map: the box must be 128 bytes wide");
+  const CUresult r = get_encode_fn()(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  if (cache.size() >= 64) cache.erase(cache.begin());
+  cache.emplace_back(key, m);
+  return m;
+}
+
+int max_tok_tiles(int EM) { return EM / 16 + 1; }
+
+struct WsLayout {
+  size_t tiles_off, count_off, status_off, gathered_off, total;
+};
+WsLayout ws_layout(int EM, int hidden) {
+  WsLayout l{};
+  size_t off = 0;
+  l.count_off = off;  off += 256;
+  l.status_off = l.count_off + 64;
+  l.tiles_off = off;  off += (size_t)max_tok_tiles(EM) * sizeof(TokTile);
+  off = (off + 1023) & ~size_t(1023);
+  l.gathered_off = off;  off += (size_t)EM * hidden * sizeof(uint16_t);
+  l.total = off;
+  return l;
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    VK_CUDA_CHECK(cudaGetDevice(&dev));
+    VK_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+    return v;
+  }();
+  return n;
+}
+
+template <bool GATEUP>
+void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+  // shared memory: 3 weight stages, scales (double-buffered when they fit), staging, barriers,
+  // the rest goes to token stages.
+  const int max_smem = 227 * 1024;
+  const int scale_tile = 128 * (p.K / 32);
+  const int fixed = 1024 + kWStages * kWStageBytes + (GATEUP ? kEpiStageBytes : 0) +
+                    (int)sizeof(Barriers) + 256;
+  int scale_bufs = 2;
+  int b_stages = (max_smem - fixed - 2 * scale_tile) / kBStageBytes;
+  if (b_stages < 3) {
+    scale_bufs = 1;
+    b_stages = (max_smem - fixed - scale_tile) / kBStageBytes;
+  }
+  expects(b_stages >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
+  if (b_stages > 8) b_stages = 8;
+  p.b_stages = b_stages;
+  p.scale_bufs = scale_bufs;
+  p.scale_buf_bytes = (scale_tile + 127) & ~127;
+  const int smem = fixed + scale_bufs * p.scale_buf_bytes + b_stages * kBStageBytes;
+  static int configured[2] = {0, 0};
+  if (configured[GATEUP] < smem) {
+    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    configured[GATEUP] = max_smem;
+  }
+  moe_gemm_sm100_kernel<GATEUP><<<sm_count(), kThreads, smem, stream>>>(tw, tb, p);
+}
+
+}  // namespace
+
+size_t sm100_workspace_bytes(int EM, int hidden, int /*ispp*/) { return ws_layout(EM, hidden).total; }
+// ---------------------------------------------------------------------------
+// optional per-kernel timing: CUDA events recorded around the two GEMM kernels
+// on the launch stream (no synchronisation while recording), summed on demand.
+// The counterpart of the reference's VK_MOE_KTIME switch
+// (src/c/vkernels/kernels/moe_fused.hip:1482-1493), without serialising stages.
+// ---------------------------------------------------------------------------
+namespace {
+struct KernelTimer {
+  bool on = false;
+  std::vector<cudaEvent_t> ev;  // 3 per call: before gate/up, between, after down
+  size_t used = 0;
+} g_timer;
+std::mutex g_timer_mu;
+}  // namespace
+
+void timing_begin(int max_calls) {
+  std::lock_guard<std::mutex> lock(g_timer_mu);
+  while (g_timer.ev.size() < (size_t)max_calls * 3) {
+    cudaEvent_t e;
+    VK_CUDA_CHECK(cudaEventCreate(&e));
+    g_timer.ev.push_back(e);
+  }
+  g_timer.used = 0;
+  g_timer.on = true;
+}
+
+void timing_end(float* gateup_ms, float* down_ms, int* calls) {
+  std::lock_guard<std::mutex> lock(g_timer_mu);
+  g_timer.on = false;
+  float g = 0.f, d = 0.f;
+  const size_t n = g_timer.used / 3;
+  if (n > 0) VK_CUDA_CHECK(cudaEventSynchronize(g_timer.ev[n * 3 - 1]));
+  for (size_t i = 0; i < n; ++i) {
+    float a = 0.f, b = 0.f;
+    VK_CUDA_CHECK(cudaEventElapsedTime(&a, g_timer.ev[3 * i], g_timer.ev[3 * i + 1]));
+    VK_CUDA_CHECK(cudaEventElapsedTime(&b, g_timer.ev[3 * i + 1], g_timer.ev[3 * i + 2]));
+    g += a;
+    d += b;
+  }
+  if (gateup_ms) *gateup_ms = g;
+  if (down_ms) *down_ms = d;
+  if (calls) *calls = (int)n;
+}
+
+namespace {
+// Records event `which` (0, 1, 2) of the current call when timing is on.
+void timer_mark(int which, cudaStream_t stream) {
+  if (!g_timer.on) return;
+  std::lock_guard<std::mutex> lock(g_timer_mu);
+  if (!g_timer.on) return;
+  // used counts recorded events; a call's three events are consecutive
+  if (g_timer.used % 3 != (size_t)which || g_timer.used >= g_timer.ev.size()) return;
+  cudaEventRecord(g_timer.ev[g_timer.used], stream);
+  g_timer.used += 1;
+}
+}  // namespace
+
+
+// Status of the most recent tcgen05 launches on the current device: 0, or
+// 100 + the code of the wait that ran out. Synchronises the device.
+int sm100_last_status() {
+  int v = 0;
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(4096));
+  VK_CUDA_CHECK(cudaDeviceSynchronize());
+  VK_CUDA_CHECK(cudaMemcpy(&v, ws + 64, sizeof(int), cudaMemcpyDeviceToHost));
+  return v;
+}
+
+void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                      const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                      int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
+                      int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                      float swiglu_limit, int activation, float beta, float linear_beta,
+                      const float* b13, const float* b2, int block_size, cudaStream_t stream) {
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  expects(aligned16(A) && aligned16(w13) && aligned16(w13_scale) && aligned16(w2) &&
+              aligned16(w2_scale) && aligned16(act_scratch),
+          "fused_moe_mxfp4: A, weights, scales and act_scratch must be 16-byte aligned");
+  const WsLayout l = ws_layout(EM, hidden);
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total));
+  TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
+  int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);
+  int* status = reinterpret_cast<int*>(ws + l.status_off);
+  uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
+
+  // The number of experts is not an argument of the layer; the tensor maps
+  // cover the rows of every expert id that fits an int32 row index.
+  const uint64_t w13_rows_cap = (uint64_t)1 << 31;
+  build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, tiles,
+                                             n_tiles, max_tok_tiles(EM));
+  gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, sorted_ids, expert_ids, block_size, EM,
+                                                       M * top_k, top_k, hidden, gathered);
+
+  GemmParams g{};
+  g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles; g.status = status;
+  g.N = M * top_k; g.top_k = top_k; g.w_sorted = w_sorted; g.activation = activation;
+  g.limit = swiglu_limit; g.beta = beta; g.linear_beta = linear_beta;
+
+  {  // gate/up
+    GemmParams p = g;
+    p.w_scale = w13_scale; p.bias = b13; p.act = act_scratch;
+    p.K = hidden; p.n_feat = ispp; p.n_ftiles = ispp / 64;
+    const CUtensorMap tw = make_map(w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, hidden / 2,
+                                    w13_rows_cap, hidden / 2, 128, 64);
+    const CUtensorMap tb = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
+                                    (uint64_t)hidden * 2, 64, 16);
+    timer_mark(0, stream);
+    launch_gemm<true>(tw, tb, p, stream);
+    timer_mark(1, stream);
+  }
+  {  // down + combine
+    GemmParams p = g;
+    p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out;
+    p.K = ispp; p.n_feat = hidden; p.n_ftiles = (hidden + 127) / 128;
+    const CUtensorMap tw = make_map(w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ispp / 2, w13_rows_cap,
+                                    ispp / 2, 128, 64);
+    const CUtensorMap tb = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
+                                    (uint64_t)ispp * 2, 64, 16);
+    launch_gemm<false>(tw, tb, p, stream);
+    timer_mark(2, stream);
+  }
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace vkernels::kernels::cuda

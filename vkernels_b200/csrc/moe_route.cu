@@ -1,0 +1,274 @@
+// moe_route.cu - router of the fused MoE layer: fp32 logits GEMM and top-k.
+//
+// The reference has no router inside moe_fused; the semantics here follow its
+// GPU routing ops: softmax top-k with renormalised weights
+// (src/python/vkernels/torch_ops/tokenspeed_amd/routing.py:58-145) and
+// sigmoid + bias selection with unbiased weights
+// (src/python/vkernels/torch_ops/glm_router.py:43-88,184-201). Ties go to the
+// lowest expert index and ids come out in descending order of selection value.
+// Group limiting (n_group > 1) is outside what the reference implements; the
+// rule used is the DeepSeek-V3 one: a group's score is the sum of its two
+// largest biased scores and only experts of the topk_group best groups stay
+// eligible.
+#include "common.cuh"
+#include "moe_fused.hpp"
+
+namespace vkernels::kernels::cuda {
+
+namespace {
+
+// ----------------------------- logits ---------------------------------------
+// logits[T, E] = x[T, H] (bf16) * wr[E, H]^T (fp32), fp32 accumulate.
+// 64 x 64 output tile per CTA, 256 threads, 4 x 4 outputs per thread,
+// K staged through shared memory 32 at a time.
+constexpr int RT = 64, RE = 64, RK = 32;
+
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ wr,
+                     float* __restrict__ logits, int T, int H, int E) {
+  __shared__ float xs[RK][RT + 4];
+  __shared__ float ws[RK][RE + 4];
+  const int tid = threadIdx.x;
+  const int t0 = blockIdx.x * RT, e0 = blockIdx.y * RE;
+  const int tx = tid & 15, ty = tid >> 4;  // tx -> experts, ty -> tokens
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < H; k0 += RK) {
+    // 64 rows x 32 k: thread loads row = tid / 4, 8 consecutive k
+    {
+      const int r = tid >> 2, kk = (tid & 3) * 8;
+      const int t = t0 + r, e = e0 + r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + kk + j;
+        xs[kk + j][r] = (t < T && k < H) ? bf16_bits_to_f32(x[(size_t)t * H + k]) : 0.0f;
+        ws[kk + j][r] = (e < E && k < H) ? wr[(size_t)e * H + k] : 0.0f;
+      }
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < RK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty * 4 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + tx * 4 + j;
+      if (e < E) logits[(size_t)t * E + e] = acc[i][j];
+    }
+  }
+}
+
+// ----------------------------- top-k ----------------------------------------
+// One warp per token. Expert e lives in lane e % 32, slot e / 32.
+constexpr int kMaxSlots = 32;  // E <= 1024
+
+struct Best {
+  float v;
+  int i;
+};
+// larger value wins; equal values: lower index wins
+__device__ __forceinline__ Best better(Best a, Best b) {
+  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+__device__ __forceinline__ Best warp_best(Best x) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    Best o{__shfl_xor_sync(0xFFFFFFFFu, x.v, d), __shfl_xor_sync(0xFFFFFFFFu, x.i, d)};
+    x = better(x, o);
+  }
+  return x;
+}
+
+template <int SLOTS>
+__global__ void __launch_bounds__(128)
+route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E,
+                  int k, int sigmoid, int n_group, int topk_group, int renorm, float scaling,
+                  int n_shared, int32_t* __restrict__ ids, float* __restrict__ w) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float NEG = -INFINITY;
+  float score[SLOTS], choice[SLOTS];
+  const float* l = logits + (size_t)t * E;
+  if (!sigmoid) {
+    float mx = NEG;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      score[s] = (e < E) ? l[e] : NEG;
+      mx = fmaxf(mx, score[s]);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+    float den = 0.0f;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      score[s] = (e < E) ? expf(score[s] - mx) : 0.0f;
+      den += score[s];
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, d);
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      score[s] = score[s] / den;
+      choice[s] = (e < E) ? (bias ? score[s] + bias[e] : score[s]) : NEG;
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      if (e < E) {
+        score[s] = 1.0f / (1.0f + expf(-l[e]));
+        choice[s] = score[s] + (bias ? bias[e] : 0.0f);
+      } else {
+        score[s] = 0.0f;
+        choice[s] = NEG;
+      }
+    }
+    if (n_group > 1) {
+      const int gs = E / n_group;
+      // group score = sum of the two largest choices of the group
+      // (lane g keeps group g's score; n_group <= 32)
+      float my_gscore = NEG;
+      for (int g = 0; g < n_group; ++g) {
+        float a = NEG, b = NEG;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+          const int e = s * 32 + lane;
+          if (e < E && e / gs == g) {
+            const float c = choice[s];
+            if (c > a) { b = a; a = c; } else if (c > b) { b = c; }
+          }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+          const float oa = __shfl_xor_sync(0xFFFFFFFFu, a, d);
+          const float ob = __shfl_xor_sync(0xFFFFFFFFu, b, d);
+          // merge two (largest, second) pairs
+          const float na = fmaxf(a, oa);
+          const float nb = fmaxf(fminf(a, oa), fmaxf(b, ob));
+          a = na;
+          b = nb;
+        }
+        const float gsc = (gs >= 2) ? a + b : a;
+        if (lane == g) my_gscore = gsc;
+      }
+      unsigned keep = 0;  // bit g set = group g stays eligible
+      for (int r = 0; r < topk_group; ++r) {
+        // a taken group competes with index INT_MAX so it cannot win again
+        const bool open = lane < n_group && !((keep >> lane) & 1u);
+        Best x = warp_best(Best{open ? my_gscore : NEG, open ? lane : 0x7FFFFFFF});
+        if (x.i < n_group) keep |= 1u << x.i;
+      }
+#pragma unroll
+      for (int s = 0; s < SLOTS; ++s) {
+        const int e = s * 32 + lane;
+        if (e < E && !((keep >> (e / gs)) & 1u)) choice[s] = NEG;
+      }
+    }
+  }
+  // k rounds of arg-max with removal
+  const int kk = k + n_shared;
+  float sum = 0.0f;
+  float my_w = 0.0f;  // lane r keeps the weight of pick r (k <= 32)
+  int my_id = 0;
+  unsigned used = 0;  // bit s set = this lane's slot s already picked
+  for (int r = 0; r < k; ++r) {
+    Best x{NEG, 0x7FFFFFFF};
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      if (e < E && !((used >> s) & 1u)) x = better(x, Best{choice[s], e});
+    }
+    x = warp_best(x);
+    float sc = 0.0f;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s)
+      if (s * 32 + lane == x.i) {
+        used |= 1u << s;
+        sc = score[s];
+      }
+    sc = __shfl_sync(0xFFFFFFFFu, sc, x.i & 31);
+    sum += sc;  // same order on every lane: pick 0, pick 1, ...
+    if (lane == r) {
+      my_w = sc;
+      my_id = x.i;
+    }
+  }
+  if (renorm) {
+    if (sigmoid) {
+      my_w = my_w / (sum + 1.0e-20f);
+    } else {
+      if (sum == 0.0f) sum = 1.0f;
+      my_w = my_w / sum;
+    }
+  }
+  my_w *= scaling;
+  if (lane < k) {
+    ids[(size_t)t * kk + lane] = my_id;
+    w[(size_t)t * kk + lane] = my_w;
+  } else if (lane < kk) {
+    ids[(size_t)t * kk + lane] = E + (lane - k);
+    w[(size_t)t * kk + lane] = 1.0f;
+  }
+}
+
+}  // namespace
+
+void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H, int E,
+                   void* stream) {
+  expects(T >= 0 && H > 0 && E > 0, "router_logits: bad dimensions");
+  if (T == 0) return;
+  expects(x && wr && logits, "router_logits: null buffer");
+  dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
+  router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, T, H, E);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void route_topk(const float* logits, const float* bias, int T, int E, int k, int sigmoid,
+                int n_group, int topk_group, int renorm, float scaling, int n_shared,
+                int32_t* ids, float* w, void* stream) {
+  expects(T >= 0 && E > 0 && k > 0 && k <= E, "route_topk: need 0 < k <= E");
+  expects(E <= 32 * kMaxSlots, "route_topk: at most 1024 experts");
+  expects(n_shared >= 0 && k + n_shared <= 32, "route_topk: k + n_shared must be at most 32");
+  expects(n_group >= 1 && n_group <= 32 && E % n_group == 0 && topk_group >= 1 &&
+              topk_group <= n_group,
+          "route_topk: bad group configuration");
+  expects(n_group == 1 || sigmoid, "route_topk: group limiting needs the sigmoid router");
+  expects(n_group == 1 || (E / n_group) * topk_group >= k,
+          "route_topk: kept groups hold fewer than k experts");
+  if (T == 0) return;
+  expects(logits && ids && w, "route_topk: null buffer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int warps = 4;
+  dim3 grid((T + warps - 1) / warps);
+  const int slots = (E + 31) / 32;
+#define VK_ROUTE(S)                                                                          \
+  route_topk_kernel<S><<<grid, warps * 32, 0, s>>>(logits, bias, T, E, k, sigmoid, n_group,   \
+                                                   topk_group, renorm, scaling, n_shared, ids, w)
+  if (slots <= 1) VK_ROUTE(1);
+  else if (slots <= 2) VK_ROUTE(2);
+  else if (slots <= 4) VK_ROUTE(4);
+  else if (slots <= 8) VK_ROUTE(8);
+  else if (slots <= 16) VK_ROUTE(16);
+  else VK_ROUTE(32);
+#undef VK_ROUTE
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace vkernels::kernels::cuda
