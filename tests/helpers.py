@@ -29,9 +29,12 @@ def bf2f(u16) -> np.ndarray:
 
 
 def round_to_bf16_f32(x: np.ndarray) -> np.ndarray:
-    b = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    """RNE to bf16, returned as fp32; NaN stays NaN whatever its payload."""
+    x = np.ascontiguousarray(x, np.float32)
+    b = x.view(np.uint32).astype(np.uint64)
     b = b + 0x7FFF + ((b >> 16) & 1)
-    return ((b >> 16).astype(np.uint32) << 16).view(np.float32)
+    r = ((b >> 16).astype(np.uint32) << 16).view(np.float32)
+    return np.where(np.isnan(x), np.float32(np.nan), r)
 
 
 def e2m1_nibble(v: float) -> int:
@@ -60,20 +63,41 @@ def uniform_problem(M=16, hidden=128, ispp=64, E=1, a=1.0, w13_byte=None, w2_byt
     return A, w13, w13s, w2, w2s
 
 
-def assert_close_bf16(got_f32: np.ndarray, ref_f32: np.ndarray, what=""):
-    """The layer's output gate, applied after rounding both sides to bf16."""
-    g = round_to_bf16_f32(got_f32).astype(np.float64)
-    r = round_to_bf16_f32(ref_f32).astype(np.float64)
-    assert np.array_equal(np.isnan(g), np.isnan(r)), f"{what}: NaN masks differ"
-    assert np.array_equal(np.isinf(g), np.isinf(r)), f"{what}: inf masks differ"
-    fin = np.isfinite(r)
+def bf16_ulp(x: np.ndarray) -> np.ndarray:
+    """Spacing of bf16 (8 significant bits) at |x|."""
+    ax = np.maximum(np.abs(x.astype(np.float64)), 2.0 ** -126)
+    return 2.0 ** (np.floor(np.log2(ax)) - 7)
+
+
+def assert_close_bf16(got_f32: np.ndarray, ref_f32: np.ndarray, what="", got_is_bf16=False):
+    """The layer's output gate against the CPU oracle (fp32 accumulation order differs):
+
+    * NaN and inf masks equal;
+    * fp32 accumulators: max-abs <= 2e-2 (skipped when `got` was already rounded to bf16);
+    * bf16 outputs: every element within max(2e-2, one bf16 ulp of the reference) - two fp32
+      values a hair apart can round to neighbouring bf16 values, and above |x| = 4 one bf16 ulp
+      already exceeds 2e-2;
+    * relative L2 of the bf16 outputs <= 1e-2.
+    """
+    got_f32 = np.asarray(got_f32, np.float32)
+    ref_f32 = np.asarray(ref_f32, np.float32)
+    assert np.array_equal(np.isnan(got_f32), np.isnan(ref_f32)), f"{what}: NaN masks differ"
+    assert np.array_equal(np.isinf(got_f32), np.isinf(ref_f32)), f"{what}: inf masks differ"
+    fin = np.isfinite(ref_f32)
     if not fin.any():
         return 0.0, 0.0
-    max_abs = float(np.max(np.abs(g[fin] - r[fin])))
-    rel_l2 = float(np.linalg.norm(g[fin] - r[fin]) / max(np.linalg.norm(r[fin]), 1e-30))
-    assert max_abs <= MAX_ABS_TOL, f"{what}: max-abs {max_abs:.3e} > {MAX_ABS_TOL}"
+    if not got_is_bf16:
+        acc_err = float(np.max(np.abs(got_f32[fin].astype(np.float64) - ref_f32[fin])))
+        assert acc_err <= MAX_ABS_TOL, f"{what}: fp32 max-abs {acc_err:.3e} > {MAX_ABS_TOL}"
+    g = round_to_bf16_f32(got_f32)[fin].astype(np.float64)
+    r = round_to_bf16_f32(ref_f32)[fin].astype(np.float64)
+    d = np.abs(g - r)
+    allowed = np.maximum(MAX_ABS_TOL, bf16_ulp(r))
+    worst = int(np.argmax(d - allowed))
+    assert (d <= allowed).all(), f"{what}: bf16 diff {d[worst]:.3e} at |ref|={abs(r[worst]):.3f} exceeds {allowed[worst]:.3e}"
+    rel_l2 = float(np.linalg.norm(g - r) / max(np.linalg.norm(r), 1e-30))
     assert rel_l2 <= REL_L2_TOL, f"{what}: rel-L2 {rel_l2:.3e} > {REL_L2_TOL}"
-    return max_abs, rel_l2
+    return float(d.max()), rel_l2
 
 
 def expand_expert_ids(expert_ids: np.ndarray, block_size: int) -> np.ndarray:

@@ -1,0 +1,133 @@
+"""The expert-parallel exchange logic on CPU ranks (gloo, world size 2 and 3): counts, variable
+all-to-all splits, row bookkeeping and the rank-ordered combine, with the device steps replaced
+by a numpy stand-in and the CPU oracle as the local experts. The sum over ranks must equal the
+single-rank oracle, and the reference's own EP forward (dist_moe.cpp:276-328)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class NumpyBackend:
+    """CPU stand-in for vkernels_b200.dist.CudaBackend (same contract, no GPU)."""
+
+    def __init__(self, weights, num_experts, rank, world):
+        from vkernels_b200.dist import ep_plan
+        self.w = weights
+        self.b, self.e = ep_plan(num_experts, world, rank)
+
+    def pack(self, x, ids, w, n_shared, world, rank, begins, cursor, row_of, send_x, send_ids, send_w, phase):
+        T, k = ids.shape
+        bg = begins.tolist()
+        for t in range(T):
+            need = {rank} if n_shared else set()
+            for j in range(k):
+                e = int(ids[t, j])
+                if 0 <= e < bg[-1]:
+                    need.add(max(r for r in range(world) if bg[r] <= e))
+            for d in range(world):
+                if d not in need:
+                    if phase == 1:
+                        row_of[t, d] = -1
+                    continue
+                row = int(cursor[d])
+                cursor[d] += 1
+                if phase == 0:
+                    continue
+                row_of[t, d] = row
+                send_x[row] = x[t]
+                for j in range(k + n_shared):
+                    if j < k:
+                        e = int(ids[t, j])
+                        own = bg[d] <= e < bg[d + 1]
+                        send_ids[row, j] = e - bg[d] if own else -1
+                        send_w[row, j] = float(w[t, j]) if own else 0.0
+                    else:
+                        send_ids[row, j] = (bg[d + 1] - bg[d]) + (j - k) if d == rank else -1
+                        send_w[row, j] = 1.0 if d == rank else 0.0
+
+    def experts(self, rows, ids, w):
+        import oracle
+        A = rows.view(torch.int16).numpy().view(np.uint16)
+        sl = slice(self.b, self.e)
+        out = oracle.moe_layer(A, self.w["w13"][sl], self.w["w13_scale"][sl], self.w["w2"][sl], self.w["w2_scale"][sl],
+                               ids.numpy(), w.numpy(), num_experts=self.e - self.b)
+        return torch.from_numpy(out)
+
+    def combine(self, back_rows, row_of, T, H, world, out):
+        acc = torch.zeros((T, H), dtype=torch.float32)
+        for d in range(world):
+            r = row_of[:, d].long()
+            m = r >= 0
+            acc[m] += back_rows[r[m]]
+        out.copy_(acc.to(out.dtype))
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from helpers import bf16_to_u16
+        from vkernels_b200 import synthetic as syn
+        from vkernels_b200.dist import ExpertParallelMoE
+
+        cfg = syn.scaled(syn.CONFIGS["c0"], H=128, I=64, E=7, top_k=3)
+        w = {k: v.numpy() for k, v in syn.make_expert_weights(cfg).items()}
+        T = 12 * world
+        A = syn.make_activations(cfg, T)
+        rng = np.random.default_rng(5)
+        ids = np.stack([rng.permutation(cfg.E)[: cfg.top_k] for _ in range(T)]).astype(np.int32)
+        tw = rng.random((T, cfg.top_k), dtype=np.float32)
+        lo, hi = rank * 12, (rank + 1) * 12
+        layer = ExpertParallelMoE(NumpyBackend(w, cfg.E, rank, world), num_experts=cfg.E, top_k=cfg.top_k,
+                                  hidden=cfg.H, rank=rank, world=world)
+        y = layer(A[lo:hi].contiguous(), topk=(torch.from_numpy(ids[lo:hi]), torch.from_numpy(tw[lo:hi])))
+        full = oracle.moe_layer(bf16_to_u16(A), w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], ids, tw,
+                                num_experts=cfg.E)
+        err = float(np.max(np.abs(y.float().numpy() - full[lo:hi])))
+        scale = float(np.abs(full).max())
+        stats = layer.last_stats()
+        ok = err <= 2 ** -7 * max(scale, 1.0) and stats["rows_sent"] >= 12 and stats["rows_sent"] <= 12 * world
+        if oracle.have_reference() and rank == 0:
+            outs = oracle.fused_moe_mxfp4_ep_reference(bf16_to_u16(A), w["w13"], w["w13_scale"], w["w2"],
+                                                       w["w2_scale"], ids, tw, num_experts=cfg.E, ep=world)
+            ok = ok and float(np.max(np.abs(outs.sum(0)[lo:hi] - y.float().numpy()))) <= 2 ** -7 * max(scale, 1.0)
+        open(os.path.join(tmp, f"rank{rank}.txt"), "w").write(f"{int(ok)} err={err} scale={scale} {stats}")
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_ep_exchange_on_gloo_ranks(world, tmp_path, oracle_mod):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        txt = (tmp_path / f"rank{r}.txt").read_text()
+        assert txt.startswith("1"), f"rank {r}: {txt}"
+
+
+def test_ep_plan_matches_oracle(oracle_mod):
+    from vkernels_b200.dist import ep_plan, expert_begins
+    for E, ep in [(8, 2), (7, 3), (128, 8), (257, 8), (5, 5)]:
+        for r in range(ep):
+            assert ep_plan(E, ep, r) == oracle_mod.moe_ep_plan(E, ep, r)
+        assert expert_begins(E, ep)[-1] == E
+    with pytest.raises(ValueError):
+        ep_plan(4, 8, 0)

@@ -249,9 +249,9 @@ def test_layer_object_end_to_end():
     y = layer(A)
     ids_np, tw_np, margin = oracle_route(cfg, A, r)
     ref = oracle_layer(A, w, torch.from_numpy(ids_np), torch.from_numpy(tw_np))
-    ok = margin > 1e-4
-    assert_close_bf16(to_np(y.float())[ok], ref[ok], "layer object")
+    ok = margin > 2e-5
+    assert_close_bf16(to_np(y.float())[ok], ref[ok], "layer object", got_is_bf16=True)
     xh = A.cpu().pin_memory()
     yh = torch.empty((64, cfg.H), dtype=torch.bfloat16).pin_memory()
     layer.forward_host(xh, yh)
-    assert torch.equal(yh, y.cpu())
+    assert_close_bf16(yh.float().numpy()[ok], ref[ok], "layer object, pinned host entry", got_is_bf16=True)

@@ -132,8 +132,10 @@ def _check_route(cfg, T, logits=None, seed=None):
                             n_group=cfg.n_group, topk_group=cfg.topk_group, renorm=cfg.renorm,
                             scaling=cfg.scaling, n_shared=cfg.shared_experts)
     rid, rw, margin = oracle_route(cfg, A, r, logits=ref_logits)
-    ok = margin > 1e-4   # tokens whose pick is decided by more than fp32 reassociation noise
-    assert ok.mean() > 0.97, f"only {ok.mean():.3f} of the tokens are well separated"
+    # tokens whose every pick is decided by more than fp32 reassociation noise (the device sums
+    # the logits and the softmax denominator in another order; observed differences are ~1e-6)
+    ok = margin > 2e-5
+    assert ok.mean() > 0.9, f"only {ok.mean():.3f} of the tokens are well separated"
     assert np.array_equal(to_np(ids)[ok], rid[ok]), "routing indices differ"
     assert np.allclose(to_np(w)[ok], rw[ok], rtol=1e-4, atol=1e-6)
     return int((~ok).sum())

@@ -56,8 +56,6 @@ constexpr int kWStages = 3;
 constexpr int kAStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kBStageBytes = kMaxTok * 128;        // 32 KB
-constexpr int kStageRowPad = 129;                  // fp32 row pitch of the epilogue staging
-constexpr int kEpiStageBytes = 32 * kStageRowPad * 4;
 constexpr int kThreads = 512;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
@@ -176,12 +174,16 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
       "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+      "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+      "r"(v[30]), "r"(v[31])
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() {
@@ -252,9 +254,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint8_t* w_smem = smem;                                      // kWStages x 16 KB
   uint8_t* b_smem = w_smem + kWStages * kWStageBytes;          // b_stages x 32 KB
   uint8_t* sc_smem = b_smem + p.b_stages * kBStageBytes;       // scale_bufs x scale_buf_bytes
-  float* epi_stage = reinterpret_cast<float*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
-  Barriers* bars = reinterpret_cast<Barriers*>(reinterpret_cast<uint8_t*>(epi_stage) +
-                                               (GATEUP ? kEpiStageBytes : 0));
+  Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
@@ -265,7 +265,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->w_empty[i]), 8);
     }
     for (int i = 0; i < kAStages; ++i) {
-      mbar_init(smem_u32(&bars->a_full[i]), 8);
+      mbar_init(smem_u32(&bars->a_full[i]), 4);
       mbar_init(smem_u32(&bars->a_empty[i]), 1);
     }
     for (int i = 0; i < 8; ++i) {
@@ -398,10 +398,31 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------ dequant --------------------------------
-    const int q = warp & 3, h = (warp - 4) >> 2;   // TMEM lane quarter, K half of a 64-K stage
-    const int row = q * 32 + lane;                 // weight row inside the item
+    // Warp (q, h): TMEM lane quarter q; of the 64-K A stages it takes those with
+    // stage counter % 2 == h, a full stage (32 columns) at a time. The tcgen05.st
+    // of one stage is left in flight while the next stage of this warp is
+    // decoded into the other register set; its completion is awaited, and the
+    // stage handed to the MMA warp, just before the next store.
+    const int q = warp & 3, h = (warp - 4) >> 2;
+    const int row = q * 32 + lane;                 // TMEM lane of this thread
+    // gate/up items interleave the two halves: even lanes hold gate rows, odd
+    // lanes the matching up rows, so the epilogue pairs them with one shuffle.
+    const int srow = GATEUP ? ((row & 1) * 64 + (row >> 1)) : row;   // row inside the staged tile
+    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols;
     uint32_t w_it = 0, a_it = 0, sc_it = 0;
+    uint32_t va[32], vb[32];
+    int pending = -1;   // A stage whose store is still in flight
+    uint32_t flip = 0;
     bool ok = true;
+    auto retire = [&]() {
+      if (pending >= 0) {
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[pending]));
+        pending = -1;
+      }
+    };
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const int f = item % p.n_ftiles;
       const int rows_valid = GATEUP ? 128 : min(128, p.n_feat - f * 128);
@@ -410,17 +431,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         ok = false;
         break;
       }
-      const uint8_t* my_scales = sc_smem + sbuf * p.scale_buf_bytes + row * pitch;
+      const uint8_t* my_scales = sc_smem + sbuf * p.scale_buf_bytes + srow * pitch;
       for (int kw = 0; kw < n_kw && ok; ++kw) {
         const int sw = w_it % kWStages;
         if (!mbar_wait(smem_u32(&bars->w_full[sw]), (w_it / kWStages) & 1u, abort_flag, 8)) {
           ok = false;
           break;
         }
-        const uint8_t* my_row = w_smem + sw * kWStageBytes + (row >> 6) * (kWStageBytes / 2) +
-                                (row & 63) * 128;
+        const uint8_t* my_row = w_smem + sw * kWStageBytes + (srow >> 6) * (kWStageBytes / 2) +
+                                (srow & 63) * 128;
         const int n_sub = min(4, n_sub_total - kw * 4);
-        for (int j = 0; j < n_sub; ++j) {
+        for (int j = 0; j < n_sub; ++j, ++a_it) {
+          if ((a_it & 1u) != (uint32_t)h) continue;
           const int sa = a_it % kAStages;
           if (!mbar_wait(smem_u32(&bars->a_empty[sa]), ((a_it / kAStages) & 1u) ^ 1u, abort_flag,
                          9)) {
@@ -428,25 +450,29 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             break;
           }
           tc_fence_after();
-          uint32_t v[16];
-          if (row < rows_valid) {
-            const int chunk = j * 2 + h;  // 16-byte chunk = 32 K elements = one scale group
-            const uint4 pk = *reinterpret_cast<const uint4*>(my_row + ((chunk ^ (row & 7)) << 4));
-            const uint32_t sc2 = ue8m0_to_bf16x2(my_scales[kw * 8 + chunk]);
-            dequant8(pk.x, sc2, v + 0);
-            dequant8(pk.y, sc2, v + 4);
-            dequant8(pk.z, sc2, v + 8);
-            dequant8(pk.w, sc2, v + 12);
+          uint32_t* v = flip ? vb : va;
+          if (srow < rows_valid) {
+            const int c0 = j * 2;   // two 16-byte chunks = two scale groups of 32 K elements
+            const uint4 p0 = *reinterpret_cast<const uint4*>(my_row + (((c0) ^ (srow & 7)) << 4));
+            const uint4 p1 = *reinterpret_cast<const uint4*>(my_row + (((c0 + 1) ^ (srow & 7)) << 4));
+            const uint32_t s0 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0]);
+            const uint32_t s1 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0 + 1]);
+            dequant8(p0.x, s0, v + 0);
+            dequant8(p0.y, s0, v + 4);
+            dequant8(p0.z, s0, v + 8);
+            dequant8(p0.w, s0, v + 12);
+            dequant8(p1.x, s1, v + 16);
+            dequant8(p1.y, s1, v + 20);
+            dequant8(p1.z, s1, v + 24);
+            dequant8(p1.w, s1, v + 28);
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = 0u;
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          tc_st16(tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols + sa * 32 + h * 16, v);
-          tc_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[sa]));
-          ++a_it;
+          retire();
+          tc_st32(t_row + sa * 32, v);
+          pending = sa;
+          flip ^= 1u;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->w_empty[sw]));
@@ -456,6 +482,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (lane == 0) mbar_arrive(smem_u32(&bars->sc_empty[sbuf]));
       ++sc_it;
     }
+    retire();
   } else if (warp >= 12) {
     // ------------------------------ epilogue -------------------------------
     const int q = warp & 3;
@@ -477,14 +504,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       if (GATEUP) {
-        const int tok = lane, fq = q;  // second phase: token = lane, 16 features per warp
-        float bg[16], bu[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          bg[j] = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + f * 64 + fq * 16 + j] : 0.0f;
-          bu[j] = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + p.n_feat + f * 64 + fq * 16 + j]
-                         : 0.0f;
-        }
+        // lane 2i holds the gate row, lane 2i+1 the up row of feature i (see the
+        // dequant role). Per 32 columns the pair exchanges halves with one shuffle
+        // each: the even lane finishes tokens 0..15, the odd lane tokens 16..31.
+        const bool odd = lane & 1;
+        const int feat = f * 64 + q * 16 + (lane >> 1);
+        const float bg = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + feat] : 0.0f;
+        const float bu = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + p.n_feat + feat] : 0.0f;
         for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
           uint32_t v[32];
           tc_ld32(t_lane + c0, v);
@@ -494,29 +520,19 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
           }
+          const int tbase = c0 + (odd ? 16 : 0);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) epi_stage[j * kStageRowPad + etid] = __uint_as_float(v[j]);
-          named_bar_sync(2, 128);
-          const int t = c0 + tok;
-          if (t < tt.n_rows && bars->tile_tok[t] >= 0) {
-            uint32_t packed[8];
-#pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-              float r[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const float g = epi_stage[tok * kStageRowPad + fq * 16 + j + u] + bg[j + u];
-                const float up = epi_stage[tok * kStageRowPad + 64 + fq * 16 + j + u] + bu[j + u];
-                r[u] = moe_act_value(p.activation, g, up, p.limit, p.beta, p.linear_beta);
-              }
-              packed[j >> 1] = (uint32_t)f32_to_bf16_bits(r[0]) | ((uint32_t)f32_to_bf16_bits(r[1]) << 16);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(p.act + (size_t)(tt.row0 + t) * p.n_feat + f * 64 +
-                                                  fq * 16);
-            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t mine = odd ? v[16 + j] : v[j];      // my row, my tokens
+            const uint32_t give = odd ? v[j] : v[16 + j];      // my row, partner's tokens
+            const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, give, 1);
+            const float g = __uint_as_float(odd ? got : mine) + bg;
+            const float u = __uint_as_float(odd ? mine : got) + bu;
+            const int t = tbase + j;
+            if (t < tt.n_rows && bars->tile_tok[t] >= 0)
+              p.act[(size_t)(tt.row0 + t) * p.n_feat + feat] =
+                  f32_to_bf16_bits(moe_act_value(p.activation, g, u, p.limit, p.beta, p.linear_beta));
           }
-          named_bar_sync(2, 128);
         }
       } else {
         const int rows_valid = min(128, p.n_feat - f * 128);
@@ -729,8 +745,7 @@ void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, GemmParams p, cud
   // the rest goes to token stages.
   const int max_smem = 227 * 1024;
   const int scale_tile = 128 * (p.K / 32);
-  const int fixed = 1024 + kWStages * kWStageBytes + (GATEUP ? kEpiStageBytes : 0) +
-                    (int)sizeof(Barriers) + 256;
+  const int fixed = 1024 + kWStages * kWStageBytes + (int)sizeof(Barriers) + 256;
   int scale_bufs = 2;
   int b_stages = (max_smem - fixed - 2 * scale_tile) / kBStageBytes;
   if (b_stages < 3) {

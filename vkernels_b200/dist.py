@@ -1,0 +1,174 @@
+"""Expert-parallel fused MXFP4 MoE over torch.distributed (NCCL on NVLink / NVSwitch).
+
+Partition: rank r owns a contiguous expert range, ``E // world`` each with the first
+``E % world`` ranks taking one more (reference src/c/vkernels/dist/dist_moe.cpp:225-240).
+Each rank owns ``T / world`` tokens and routes them locally. One layer call is
+
+  1. route the local tokens                                   (router kernels)
+  2. count the tokens that must visit each rank, exchange the counts (one small all-to-all; the
+     only host read of the step, needed for the split sizes of the variable-size exchanges)
+  3. pack one activation row per (token, destination rank) with its slots rewritten to the
+     destination's LOCAL expert ids, -1 for slots owned elsewhere - the masking rule of
+     dist_moe.cpp:242-274                                      (pack kernel)
+  4. all-to-all: activation rows (bf16) and slot metadata
+  5. the single-GPU alignment + fused layer on the received rows -> fp32 partial rows
+  6. all-to-all back: partial rows (fp32 on the wire)
+  7. per token, add the at most ``world`` returned rows in ascending rank order -> bf16
+                                                                 (combine kernel)
+
+The reference's own EP forward keeps the activations replicated and sums dense per-rank
+outputs (dist_moe.cpp:276-328); the sum over ranks computed here is the same quantity, and
+tests check it against that function. Always-on shared experts are replicated: each rank applies
+them to its own tokens as extra local experts after its routed ones.
+
+The device-side steps are reached through a small ``backend`` object so the exchange logic can be
+exercised on CPU ranks (gloo) with a stand-in backend; the default backend calls the CUDA library
+and has no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import native_runtime as nr
+
+
+def ep_plan(num_experts: int, ep: int, rank: int) -> tuple[int, int]:
+    """[begin, end) of the experts owned by `rank` (dist_moe.cpp:225-240)."""
+    if ep <= 0 or not (0 <= rank < ep) or num_experts < ep:
+        raise ValueError("ep_plan: need ep > 0, 0 <= rank < ep, num_experts >= ep")
+    base, rem = divmod(num_experts, ep)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def expert_begins(num_experts: int, ep: int) -> list[int]:
+    return [ep_plan(num_experts, ep, r)[0] for r in range(ep)] + [num_experts]
+
+
+class CudaBackend:
+    """Device steps of the EP layer on the CUDA library."""
+
+    def __init__(self, layer, device):
+        self.layer = layer          # vkernels_b200.experts.FusedMoEMxfp4 holding the LOCAL experts
+        self.device = torch.device(device)
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def route(self, x):
+        return self.layer.route(x)
+
+    def pack(self, x, ids, w, n_shared, world, rank, begins, cursor, row_of, send_x, send_ids, send_w, phase):
+        T, H = x.shape
+        p = lambda t: None if t is None else t.data_ptr()
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_pack(
+                p(x), p(ids), p(w), T, H, ids.shape[1], n_shared, world, rank, p(begins), p(cursor),
+                p(row_of), p(send_x), p(send_ids), p(send_w), phase, self._stream())
+        nr.check(rc, "ep_pack")
+
+    def experts(self, rows, ids, w):
+        """fp32 [R, H]: the local experts applied to received rows."""
+        return self.layer.experts_fp32(rows, ids, w)
+
+    def combine(self, back_rows, row_of, T, H, world, out):
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_combine(back_rows.data_ptr(), row_of.data_ptr(), T, H, world,
+                                                          out.data_ptr(), None, self._stream())
+        nr.check(rc, "ep_combine")
+
+
+class ExpertParallelMoE:
+    """One MoE layer sharded over the ranks of a process group."""
+
+    def __init__(self, backend, *, num_experts: int, top_k: int, hidden: int, n_shared: int = 0,
+                 rank: int | None = None, world: int | None = None, group=None, device="cpu"):
+        self.backend = backend
+        self.group = group
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.world = dist.get_world_size(group) if world is None else world
+        self.num_experts, self.top_k, self.hidden, self.n_shared = num_experts, top_k, hidden, n_shared
+        self.slots = top_k + n_shared
+        self.device = torch.device(device)
+        self.begins_host = expert_begins(num_experts, self.world)
+        self.begins = torch.tensor(self.begins_host, dtype=torch.int32, device=self.device)
+        self._stats = {}
+
+    @classmethod
+    def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
+        """Generates this rank's slice of the seeded weights of a benchmark configuration."""
+        from . import synthetic as syn
+        from .experts import FusedMoEMxfp4
+
+        b, e = ep_plan(cfg.E, world, rank)
+        # every rank draws the same stream and keeps its slice (+ the shared experts)
+        full = syn.make_expert_weights(cfg, seed=seed, backend="torch", device=device)
+        keep = list(range(b, e)) + list(range(cfg.E, cfg.n_weight_experts))
+        idx = torch.tensor(keep, device=device)
+        w = {k: v.index_select(0, idx).contiguous() for k, v in full.items()}
+        del full
+        torch.cuda.empty_cache()
+        r = syn.make_router(cfg, seed=seed, device=device)
+        local = FusedMoEMxfp4(w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], top_k=cfg.top_k,
+                              router_weight=r["wr"], router_bias=r["bias"], routing=cfg.routing,
+                              renorm=cfg.renorm, scaling=cfg.scaling, n_group=cfg.n_group,
+                              topk_group=cfg.topk_group, n_shared=cfg.shared_experts,
+                              swiglu_limit=cfg.swiglu_limit, max_tokens=max_tokens * world)
+        return cls(CudaBackend(local, device), num_experts=cfg.E, top_k=cfg.top_k, hidden=cfg.H,
+                   n_shared=cfg.shared_experts, rank=rank, world=world, group=group, device=device)
+
+    def last_stats(self) -> dict:
+        return dict(self._stats)
+
+    def forward(self, x: torch.Tensor, topk=None) -> torch.Tensor:
+        """x [T_local, H] bf16 -> bf16 [T_local, H]. `topk` = (ids [T, k] int32 GLOBAL expert ids,
+        weights [T, k] fp32) skips the router."""
+        T, H = x.shape
+        world, rank, slots = self.world, self.rank, self.slots
+        dev = x.device
+        if topk is None:
+            ids, w = self.backend.route(x)
+            ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
+        else:
+            ids, w = topk
+        # 2. counts
+        counts = torch.zeros(world, dtype=torch.int32, device=dev)
+        self.backend.pack(x, ids, w, self.n_shared, world, rank, self.begins, counts, None, None, None, None, 0)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)
+        both = torch.stack([counts, recv_counts]).cpu()          # the step's one host read
+        send_n, recv_n = both[0].tolist(), both[1].tolist()
+        R_send, R_recv = sum(send_n), sum(recv_n)
+        # 3. pack
+        cursor = (torch.cumsum(counts, 0) - counts).to(torch.int32)
+        row_of = torch.empty((T, world), dtype=torch.int32, device=dev)
+        send_x = torch.empty((max(R_send, 1), H), dtype=x.dtype, device=dev)
+        send_ids = torch.empty((max(R_send, 1), slots), dtype=torch.int32, device=dev)
+        send_w = torch.empty((max(R_send, 1), slots), dtype=torch.float32, device=dev)
+        self.backend.pack(x, ids, w, self.n_shared, world, rank, self.begins, cursor, row_of, send_x,
+                          send_ids, send_w, 1)
+        # 4. dispatch
+        recv_x = torch.empty((max(R_recv, 1), H), dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv_x[:R_recv], send_x[:R_send], recv_n, send_n, group=self.group)
+        recv_ids = torch.empty((max(R_recv, 1), slots), dtype=torch.int32, device=dev)
+        recv_w = torch.empty((max(R_recv, 1), slots), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(recv_ids[:R_recv], send_ids[:R_send], recv_n, send_n, group=self.group)
+        dist.all_to_all_single(recv_w[:R_recv], send_w[:R_send], recv_n, send_n, group=self.group)
+        # 5. local experts
+        if R_recv > 0:
+            part = self.backend.experts(recv_x[:R_recv], recv_ids[:R_recv], recv_w[:R_recv])
+        else:
+            part = torch.zeros((0, H), dtype=torch.float32, device=dev)
+        # 6. return
+        back = torch.empty((max(R_send, 1), H), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(back[:R_send], part, send_n, recv_n, group=self.group)
+        # 7. combine
+        out = torch.empty((T, H), dtype=x.dtype, device=dev)
+        self.backend.combine(back, row_of, T, H, world, out)
+        self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T,
+                       "launches_per_step": 2 + 2 + 1 + (1 if R_recv * slots <= 1024 else 3) + 4,
+                       "dispatch_bytes": R_send * (H * 2 + slots * 8), "combine_bytes": R_recv * H * 4}
+        return out
+
+    __call__ = forward

@@ -152,7 +152,12 @@ class FusedMoEMxfp4:
                        n_shared=self.n_shared, out=(ids, w))
         return ids, w
 
-    def experts(self, x, topk_ids, topk_w, bufs=None, out_bf16=None):
+    def experts_fp32(self, x, topk_ids, topk_w):
+        """Like :meth:`experts` but returns the fp32 accumulator [T, hidden] (a view of the
+        persistent buffer: consume it before the next call)."""
+        return self.experts(x, topk_ids, topk_w, return_fp32=True)
+
+    def experts(self, x, topk_ids, topk_w, bufs=None, out_bf16=None, return_fp32=False):
         """Alignment + the two grouped GEMMs for given routing; returns bf16 [T, hidden]."""
         T = x.shape[0]
         bufs = bufs or self._buffers(T)
@@ -168,6 +173,8 @@ class FusedMoEMxfp4:
                                  swiglu_limit=self.swiglu_limit, activation=self.activation,
                                  beta=self.beta, linear_beta=self.linear_beta, b13=self.b13,
                                  b2=self.b2)
+        if return_fp32:
+            return out
         y = bufs["y"].view(T, self.hidden) if out_bf16 is None else out_bf16
         y.copy_(out)
         return y
