@@ -52,10 +52,9 @@ constexpr int kMaxTok = 256;        // tokens (MMA N) per work item
 constexpr int kRows = 128;          // weight rows (MMA M) per work item
 constexpr int kWStageK = 256;       // K elements per packed-weight stage (128 B per row)
 constexpr int kSubK = 64;           // K elements per A stage / token stage (128 B of bf16)
-constexpr int kWStages = 3;
+constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per launch (3..8)
 constexpr int kAStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
-constexpr int kBStageBytes = kMaxTok * 128;        // 32 KB
 constexpr int kThreads = 512;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
@@ -85,6 +84,9 @@ struct GemmParams {
   int top_k;
   int w_sorted;
   int b_stages;
+  int b_stage_bytes;          // max_tok * 128
+  int w_stages;
+  int max_tok;                // largest token tile of this launch (multiple of 16, <= 256)
   int scale_bufs;
   int scale_buf_bytes;
   int activation;
@@ -230,7 +232,7 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 // shared-memory carve-up
 // ---------------------------------------------------------------------------
 struct Barriers {
-  uint64_t w_full[kWStages], w_empty[kWStages];
+  uint64_t w_full[kMaxWStages], w_empty[kMaxWStages];
   uint64_t a_full[kAStages], a_empty[kAStages];
   uint64_t b_full[8], b_empty[8];
   uint64_t sc_full[2], sc_empty[2];
@@ -247,20 +249,21 @@ struct Barriers {
 template <bool GATEUP>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* w_smem = smem;                                      // kWStages x 16 KB
-  uint8_t* b_smem = w_smem + kWStages * kWStageBytes;          // b_stages x 32 KB
-  uint8_t* sc_smem = b_smem + p.b_stages * kBStageBytes;       // scale_bufs x scale_buf_bytes
+  uint8_t* w_smem = smem;                                      // w_stages x 16 KB
+  uint8_t* b_smem = w_smem + p.w_stages * kWStageBytes;        // b_stages x b_stage_bytes
+  uint8_t* sc_smem = b_smem + p.b_stages * p.b_stage_bytes;    // scale_bufs x scale_buf_bytes
   Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
   if (tid == 0) {
-    for (int i = 0; i < kWStages; ++i) {
+    for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
       mbar_init(smem_u32(&bars->w_empty[i]), 8);
     }
@@ -302,14 +305,16 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int n_wrows = GATEUP ? 2 * p.n_feat : p.n_feat;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ---------------------------
+    // ------------------- TMA producer: packed weights + scales ---------------
+    // Runs ahead of the token producer by the depth of its own ring, so the
+    // weight stream (the HBM-bound part) is never held back by token stages.
     if (lane == 0) {
-      uint32_t w_it = 0, b_it = 0, sc_it = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      uint32_t w_it = 0, sc_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const TokTile tt = p.tiles[item / p.n_ftiles];
         const int f = item % p.n_ftiles;
-        // weight rows of this item: two boxes of 64 rows
-        int row_a, row_b, rows_valid;
+        int row_a, row_b, rows_valid;   // two boxes of 64 weight rows
         if (GATEUP) {
           row_a = tt.expert * n_wrows + f * 64;
           row_b = row_a + p.n_feat;
@@ -319,7 +324,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           row_b = row_a + 64;
           rows_valid = min(128, p.n_feat - f * 128);
         }
-        // scales of the item's rows
         {
           const int sb = sc_it % p.scale_bufs;
           const uint32_t par = ((sc_it / p.scale_bufs) & 1u) ^ 1u;
@@ -333,34 +337,39 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             bulk_load_1d(dst + half, p.w_scale + (size_t)row_b * pitch, half, bar);
           ++sc_it;
         }
-        int sub = 0;
-        bool ok = true;
-        for (int kw = 0; kw < n_kw && ok; ++kw) {
-          {
-            const int s = w_it % kWStages;
-            const uint32_t par = ((w_it / kWStages) & 1u) ^ 1u;
-            if (!mbar_wait(smem_u32(&bars->w_empty[s]), par, abort_flag, 2)) { ok = false; break; }
-            const uint32_t bar = smem_u32(&bars->w_full[s]);
-            const uint32_t dst = smem_u32(w_smem + s * kWStageBytes);
-            mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
-            tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
-            if (rows_valid == 128) tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
-            ++w_it;
-          }
-          const int n_sub = min(4, n_sub_total - kw * 4);
-          for (int j = 0; j < n_sub; ++j, ++sub) {
-            const int s = b_it % p.b_stages;
-            const uint32_t par = ((b_it / p.b_stages) & 1u) ^ 1u;
-            if (!mbar_wait(smem_u32(&bars->b_empty[s]), par, abort_flag, 3)) { ok = false; break; }
-            const uint32_t bar = smem_u32(&bars->b_full[s]);
-            const uint32_t dst = smem_u32(b_smem + s * kBStageBytes);
-            mbar_expect_tx(bar, tt.n_rows * 128);
-            for (int r = 0; r < tt.n_rows; r += 16)
-              tma_load_2d(dst + r * 128, &tmap_b, sub * kSubK, tt.row0 + r, bar);
-            ++b_it;
-          }
+        for (int kw = 0; kw < n_kw; ++kw, ++w_it) {
+          const int s = w_it % p.w_stages;
+          const uint32_t par = ((w_it / p.w_stages) & 1u) ^ 1u;
+          if (!mbar_wait(smem_u32(&bars->w_empty[s]), par, abort_flag, 2)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&bars->w_full[s]);
+          const uint32_t dst = smem_u32(w_smem + s * kWStageBytes);
+          mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
+          tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
+          if (rows_valid == 128)
+            tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
         }
-        if (!ok) break;
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------- TMA producer: token tiles ---------------------------
+    if (lane == 0) {
+      uint32_t b_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const TokTile tt = p.tiles[item / p.n_ftiles];
+        for (int sub = 0; sub < n_sub_total; ++sub, ++b_it) {
+          const int s = b_it % p.b_stages;
+          const uint32_t par = ((b_it / p.b_stages) & 1u) ^ 1u;
+          if (!mbar_wait(smem_u32(&bars->b_empty[s]), par, abort_flag, 3)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&bars->b_full[s]);
+          const uint32_t dst = smem_u32(b_smem + s * p.b_stage_bytes);
+          mbar_expect_tx(bar, tt.n_rows * 128);
+          int r = 0;
+          for (; r + 64 <= tt.n_rows; r += 64)
+            tma_load_2d(dst + r * 128, &tmap_b64, sub * kSubK, tt.row0 + r, bar);
+          for (; r < tt.n_rows; r += 16)
+            tma_load_2d(dst + r * 128, &tmap_b, sub * kSubK, tt.row0 + r, bar);
+        }
       }
     }
   } else if (warp == 1) {
@@ -381,7 +390,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             break;
           }
           tc_fence_after();
-          const uint32_t b_addr = smem_u32(b_smem + sb * kBStageBytes);
+          const uint32_t b_addr = smem_u32(b_smem + sb * p.b_stage_bytes);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             tc_mma_ts(tmem_base, tmem_base + kAccCols + sa * 32 + kk * 8,
@@ -433,8 +442,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
       const uint8_t* my_scales = sc_smem + sbuf * p.scale_buf_bytes + srow * pitch;
       for (int kw = 0; kw < n_kw && ok; ++kw) {
-        const int sw = w_it % kWStages;
-        if (!mbar_wait(smem_u32(&bars->w_full[sw]), (w_it / kWStages) & 1u, abort_flag, 8)) {
+        const int sw = w_it % p.w_stages;
+        if (!mbar_wait(smem_u32(&bars->w_full[sw]), (w_it / p.w_stages) & 1u, abort_flag, 8)) {
           ok = false;
           break;
         }
@@ -583,10 +592,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
 // ---------------------------------------------------------------------------
 
 // Token tiles from expert_ids: a run of consecutive blocks with the same
-// non-negative expert becomes ceil(rows / kMaxTok) tiles of (almost) equal
+// non-negative expert becomes ceil(rows / max_tok) tiles of (almost) equal
 // size, each a multiple of 16 rows.
 __global__ void __launch_bounds__(1024)
-build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size,
+build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size, int max_tok,
                    TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
   __shared__ int scan[1024];
   __shared__ int base;
@@ -605,7 +614,7 @@ build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int blo
       }
     }
     const int rows = run_blocks * block_size;
-    const int nt = (rows + kMaxTok - 1) / kMaxTok;
+    const int nt = (rows + max_tok - 1) / max_tok;
     scan[tid] = nt;
     __syncthreads();
     for (int d = 1; d < 1024; d <<= 1) {
@@ -740,31 +749,38 @@ int sm_count() {
 }
 
 template <bool GATEUP>
-void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
-  // shared memory: 3 weight stages, scales (double-buffered when they fit), staging, barriers,
-  // the rest goes to token stages.
+void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
+                 cudaStream_t stream) {
+  // Shared memory: token stages of max_tok rows, scales (double-buffered when they fit), barriers;
+  // what is left becomes the packed-weight ring (3..8 stages of 16 KB): the deeper it is, the more
+  // weight bytes are in flight, which is what a decode-size batch is bound by.
   const int max_smem = 227 * 1024;
-  const int scale_tile = 128 * (p.K / 32);
-  const int fixed = 1024 + kWStages * kWStageBytes + (int)sizeof(Barriers) + 256;
-  int scale_bufs = 2;
-  int b_stages = (max_smem - fixed - 2 * scale_tile) / kBStageBytes;
-  if (b_stages < 3) {
-    scale_bufs = 1;
-    b_stages = (max_smem - fixed - scale_tile) / kBStageBytes;
+  const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
+  const int fixed = 1024 + (int)sizeof(Barriers) + 256;
+  p.b_stage_bytes = p.max_tok * 128;
+  int b_stages = 4, scale_bufs = 2;
+  auto w_room = [&]() { return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes; };
+  if (w_room() < 4) scale_bufs = 1;
+  if (w_room() < 3) b_stages = 3;
+  if (w_room() < 3) b_stages = 2;
+  expects(w_room() >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
+  p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
+  if (p.w_stages == kMaxWStages) {   // spare room: deepen the token ring too
+    while (b_stages < 8 && (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) /
+                                   kWStageBytes >= kMaxWStages)
+      ++b_stages;
   }
-  expects(b_stages >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
-  if (b_stages > 8) b_stages = 8;
   p.b_stages = b_stages;
   p.scale_bufs = scale_bufs;
-  p.scale_buf_bytes = (scale_tile + 127) & ~127;
-  const int smem = fixed + scale_bufs * p.scale_buf_bytes + b_stages * kBStageBytes;
-  static int configured[2] = {0, 0};
-  if (configured[GATEUP] < smem) {
+  p.scale_buf_bytes = scale_tile;
+  const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWStageBytes;
+  static bool configured[2] = {false, false};
+  if (!configured[GATEUP]) {
     VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    configured[GATEUP] = max_smem;
+    configured[GATEUP] = true;
   }
-  moe_gemm_sm100_kernel<GATEUP><<<sm_count(), kThreads, smem, stream>>>(tw, tb, p);
+  moe_gemm_sm100_kernel<GATEUP><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
 }
 
 }  // namespace
@@ -858,7 +874,11 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // The number of experts is not an argument of the layer; the tensor maps
   // cover the rows of every expert id that fits an int32 row index.
   const uint64_t w13_rows_cap = (uint64_t)1 << 31;
-  build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, tiles,
+  // A token meets an expert at most once, so no expert holds more than M rows (+ padding).
+  int max_tok = ((M + block_size - 1) / block_size) * block_size;
+  max_tok = ((max_tok + 15) / 16) * 16;
+  if (max_tok > kMaxTok) max_tok = kMaxTok;
+  build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                              n_tiles, max_tok_tiles(EM));
   gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, sorted_ids, expert_ids, block_size, EM,
                                                        M * top_k, top_k, hidden, gathered);
@@ -866,7 +886,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   GemmParams g{};
   g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles; g.status = status;
   g.N = M * top_k; g.top_k = top_k; g.w_sorted = w_sorted; g.activation = activation;
-  g.limit = swiglu_limit; g.beta = beta; g.linear_beta = linear_beta;
+  g.limit = swiglu_limit; g.beta = beta; g.linear_beta = linear_beta; g.max_tok = max_tok;
 
   {  // gate/up
     GemmParams p = g;
@@ -876,8 +896,10 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                                     w13_rows_cap, hidden / 2, 128, 64);
     const CUtensorMap tb = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
                                     (uint64_t)hidden * 2, 64, 16);
+    const CUtensorMap tb64 = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
+                                      (uint64_t)hidden * 2, 64, 64);
     timer_mark(0, stream);
-    launch_gemm<true>(tw, tb, p, stream);
+    launch_gemm<true>(tw, tb, tb64, p, stream);
     timer_mark(1, stream);
   }
   {  // down + combine
@@ -888,7 +910,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                                     ispp / 2, 128, 64);
     const CUtensorMap tb = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
                                     (uint64_t)ispp * 2, 64, 16);
-    launch_gemm<false>(tw, tb, p, stream);
+    const CUtensorMap tb64 = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
+                                      (uint64_t)ispp * 2, 64, 64);
+    launch_gemm<false>(tw, tb, tb64, p, stream);
     timer_mark(2, stream);
   }
   VK_CUDA_CHECK(cudaGetLastError());

@@ -129,20 +129,23 @@ def make_expert_weights(cfg: MoEConfig, *, codes: str = "finite", seed: int | No
         raise ValueError(f"unknown backend {backend!r}")
     g = torch.Generator(device=device)
     g.manual_seed((cfg.seed if seed is None else seed) * 7919 + 1)
-    lut = torch.from_numpy(FINITE_CODES).to(device)
     for name, shp in shapes.items():
         if name.endswith("_scale"):
             out[name] = (127 + torch.randint(lo, hi + 1, shp, generator=g, device=device,
                                              dtype=torch.int16)).to(torch.uint8)
         else:
+            # a few large launches per tensor (in slabs of at most ~1 GB of temporaries)
             t = torch.empty(shp, dtype=torch.uint8, device=device)
-            for e in range(En):
+            per = max(1, (1 << 29) // (shp[1] * shp[2]))
+            for e0 in range(0, En, per):
+                e1 = min(En, e0 + per)
+                n_codes = 12 if codes == "finite" else 16
+                c = torch.randint(0, n_codes, (2, e1 - e0) + shp[1:], generator=g, device=device,
+                                  dtype=torch.uint8)
                 if codes == "finite":
-                    c = lut[torch.randint(0, 12, (2,) + shp[1:], generator=g, device=device)]
-                else:
-                    c = torch.randint(0, 16, (2,) + shp[1:], generator=g, device=device,
-                                      dtype=torch.uint8)
-                t[e] = c[0] | (c[1] << 4)
+                    c += (c >= 6).to(torch.uint8) * 2     # 0..11 -> {0..5, 8..13}
+                t[e0:e1] = c[0] | (c[1] << 4)
+                del c
             out[name] = t
     return out
 
