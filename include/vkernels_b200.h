@@ -102,6 +102,25 @@ size_t vk_moe_align_block_size_max_em(int32_t M, int32_t top_k, int32_t block_si
 
 /* ---- additive entry points (DEVICE pointers) ------------------------------ */
 
+/* No counterpart in the reference. The alignment of vk_hip_moe_align_block_size
+ * for callers that cannot allocate device memory during a call: a server whose
+ * memory pool owns all free memory after warm-up, or a step that cannot afford
+ * the device-wide stall of cudaMalloc. The other entry point may grow the
+ * library's scratch block for large batches; this one keeps its chunk
+ * histograms in a fixed array compiled into the library (about 514 KB of
+ * device memory per GPU that loads the library, held until exit) and never
+ * allocates. Same arguments, same outputs bit for bit. Limits: M*top_k <=
+ * 262144 and local_n <= 512, otherwise VK_ERROR_INVALID_ARGUMENT with a
+ * message naming the limit. All calls on a device share the array: calls that
+ * may overlap on the GPU (different streams without ordering) race - serialise
+ * them. The first call on each device looks up the array's address; make it
+ * before starting a stream capture. */
+int vk_cuda_moe_align_block_size_noalloc(const int32_t* topk_ids, const int32_t* expert_map,
+                                         int32_t M, int32_t top_k, int32_t block_size,
+                                         int32_t num_experts, int32_t local_n, int32_t max_EM,
+                                         int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_EM,
+                                         void* stream);
+
 /* The layer with routing weights already in sorted-row order (the CPU entry
  * point's convention, moe_fused.hpp:83-101) - no reference counterpart on the
  * device side. */

@@ -109,6 +109,17 @@ int vk_hip_moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_m
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 
+int vk_cuda_moe_align_block_size_noalloc(const int32_t* topk_ids, const int32_t* expert_map,
+                                         int32_t M, int32_t top_k, int32_t block_size,
+                                         int32_t num_experts, int32_t local_n, int32_t max_EM,
+                                         int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_EM,
+                                         void* stream) {
+  VK_TRY
+  vkc::moe_align_block_size_noalloc(topk_ids, expert_map, M, top_k, block_size, num_experts,
+                                    local_n, max_EM, sorted_ids, expert_ids, out_EM, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
 int vk_cuda_fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13,
                                      const uint8_t* w13_scale, const uint8_t* w2,
                                      const uint8_t* w2_scale, const float* topk_w_sorted,

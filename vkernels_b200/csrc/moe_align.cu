@@ -239,4 +239,90 @@ void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, in
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------
+// Alignment for callers that must not allocate
+// ---------------------------------------------------------------------------
+// Some callers of this library cannot tolerate a device allocation inside a
+// call: an inference server that has handed all free memory to its own pool
+// after warm-up (a later cudaMalloc can simply fail), a latency-critical step
+// where cudaMalloc's implicit device-wide synchronisation would stall every
+// stream, or code already inside a region where allocation is forbidden. The
+// chunked alignment above takes its chunk histograms from the library
+// workspace, which may have to grow. This variant keeps them in a fixed array
+// that is part of the library image instead: every GPU that loads the library
+// holds these ~514 KB until the process exits, and nothing is ever allocated.
+//
+// Limits (rejected with std::invalid_argument beyond them):
+//   M * top_k <= kNoAllocMaxChunks * 1024 = 262144 routed slots
+//   local_n   <= kNoAllocMaxLocal      = 512 local experts
+//
+// The array is shared by every call on a device and keeps the previous call's
+// contents. The kernels overwrite each entry they later read (every chunk
+// writes its full histogram row, the scan writes every offset), so nothing
+// needs clearing between calls; two calls whose kernels overlap on the GPU
+// (different streams, no ordering) would race on it - order them.
+//
+// The first call on each device looks the array's device address up (host code
+// only sees a stand-in symbol, not an address); that first call should be made
+// before any stream capture begins.
+constexpr int kNoAllocMaxChunks = 256;
+constexpr int kNoAllocMaxLocal = 512;
+static __device__ __align__(256) int g_noalloc_align_scratch[kNoAllocMaxChunks * kNoAllocMaxLocal +
+                                                             kNoAllocMaxLocal];
+
+void moe_align_block_size_noalloc(const int32_t* topk_ids, const int32_t* expert_map, int M,
+                                  int top_k, int block_size, int num_experts, int local_n,
+                                  int max_EM, int32_t* sorted_ids, int32_t* expert_ids,
+                                  int32_t* out_em, void* stream) {
+  expects(block_size > 0, "moe_align_block_size_noalloc: block_size must be positive");
+  expects(M >= 0 && top_k >= 0 && num_experts >= 0 && local_n >= 0,
+          "moe_align_block_size_noalloc: negative dimension");
+  expects(max_EM > 0 && max_EM % block_size == 0,
+          "moe_align_block_size_noalloc: max_EM must be a positive multiple of block_size");
+  expects(local_n <= num_experts, "moe_align_block_size_noalloc: local_n exceeds num_experts");
+  expects(out_em != nullptr && sorted_ids != nullptr && expert_ids != nullptr,
+          "moe_align_block_size_noalloc: output buffers must not be null");
+  expects(M == 0 || topk_ids != nullptr, "moe_align_block_size_noalloc: topk_ids must not be null");
+  expects((long long)M * top_k <= (long long)kNoAllocMaxChunks * kChunk,
+          "moe_align_block_size_noalloc: M*top_k exceeds the fixed scratch (at most 262144 routed "
+          "slots); use vk_hip_moe_align_block_size");
+  expects(local_n <= kNoAllocMaxLocal,
+          "moe_align_block_size_noalloc: local_n exceeds the fixed scratch (at most 512 local "
+          "experts); use vk_hip_moe_align_block_size");
+  const int N = M * top_k;
+  const int ln = local_n > 0 ? local_n : 1;
+  const int n_chunks = N > 0 ? (N + kChunk - 1) / kChunk : 1;
+
+  // Device address of the array, looked up once per device with that device current.
+  static int* scratch_of_device[64] = {};
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  expects(dev >= 0 && dev < 64, "moe_align_block_size_noalloc: device index out of range");
+  if (scratch_of_device[dev] == nullptr) {
+    int* ptr = nullptr;
+    VK_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_align_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  int* hist = scratch_of_device[dev];
+  int* offset = hist + (size_t)n_chunks * ln;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t hist_smem = (size_t)(kWarps + 1) * ln * sizeof(int);
+  if (hist_smem > 48 * 1024) {
+    VK_CUDA_CHECK(cudaFuncSetAttribute(align_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)hist_smem));
+    VK_CUDA_CHECK(cudaFuncSetAttribute(align_scatter_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem));
+  }
+  align_hist_kernel<<<n_chunks, kChunk, hist_smem, s>>>(topk_ids, expert_map, N, block_size,
+                                                        num_experts, local_n, max_EM, sorted_ids,
+                                                        expert_ids, hist);
+  const size_t scan_smem = (size_t)(ln + kChunk) * sizeof(int);
+  align_scan_kernel<<<1, kChunk, scan_smem, s>>>(hist, n_chunks, local_n, block_size, max_EM,
+                                                 expert_ids, out_em, offset);
+  align_scatter_kernel<<<n_chunks, kChunk, hist_smem, s>>>(topk_ids, expert_map, N, num_experts,
+                                                           local_n, max_EM, hist, offset, sorted_ids);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
 }  // namespace vkernels::kernels::cuda

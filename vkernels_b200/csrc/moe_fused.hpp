@@ -69,6 +69,19 @@ void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, in
                           int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_em,
                           void* stream = nullptr);
 
+// The same alignment for callers that cannot allocate device memory inside a
+// call (memory pool frozen after warm-up, no tolerance for cudaMalloc's device
+// synchronisation): its scratch is a fixed ~514 KB array inside the library
+// image, so nothing is allocated, at the price of limits - at most 262144
+// routed slots (M*top_k) and 512 local experts; larger problems are rejected.
+// Calls on one device share that array: do not let two of them overlap on the
+// GPU. The first call on a device resolves the array's address and should come
+// before any stream capture.
+void moe_align_block_size_noalloc(const int32_t* topk_ids, const int32_t* expert_map, int M,
+                                  int top_k, int block_size, int num_experts, int local_n,
+                                  int max_EM, int32_t* sorted_ids, int32_t* expert_ids,
+                                  int32_t* out_em, void* stream = nullptr);
+
 // logits[t, e] = sum_k fp32(x[t, k]) * wr[e, k]   (x bf16 [T, H], wr fp32 [E, H]).
 void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H, int E,
                    void* stream);

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "vk_hip_fused_moe_mxfp4": (None, [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 2 + [c_int, c_float,
                                       c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_hip_moe_align_block_size": (c_int, [c_void_p, c_void_p] + [c_int32] * 6 + [c_void_p] * 4),
+    "vk_cuda_moe_align_block_size_noalloc": (c_int, [c_void_p, c_void_p] + [c_int32] * 6 + [c_void_p] * 4),
     "vk_fused_moe_mxfp4": (c_int32, [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_float,
                                      c_void_p, c_void_p]),
     "vk_moe_align_block_size": (c_int32, [c_void_p] + [c_int32] * 4 + [c_void_p] * 3),
