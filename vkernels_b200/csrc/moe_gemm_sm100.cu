@@ -53,10 +53,10 @@ constexpr int kRows = 128;          // weight rows (MMA M) per work item
 constexpr int kWStageK = 256;       // K elements per packed-weight stage (128 B per row)
 constexpr int kSubK = 64;           // K elements per A stage / token stage (128 B of bf16)
 constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per launch (3..8)
-constexpr int kAStages = 8;
+constexpr int kMaxAStages = 8;
+constexpr int kMaxBStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kThreads = 512;
-constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 40u * 1000u * 1000u;
 
@@ -134,6 +134,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         *abort_flag = code;
         return false;
       }
+    }
+  }
+}
+// Whole-warp wait in which each ACTIVE lane polls its own barrier in the same
+// instruction; returns once every active lane has seen its phase complete.
+__device__ __forceinline__ bool mbar_wait_lanes(uint32_t bar, uint32_t parity, bool active,
+                                                volatile int* abort_flag, int code) {
+  bool done = !active;
+  for (uint32_t it = 0;; ++it) {
+    if (!done) done = mbar_try_wait(bar, parity);
+    if (__all_sync(0xFFFFFFFFu, done)) return true;
+    if ((it & 1023u) == 1023u) {
+      int stop = *abort_flag;
+      if (!stop && it > kSpinLimit) {
+        *abort_flag = code;
+        stop = 1;
+      }
+      if (__any_sync(0xFFFFFFFFu, stop != 0)) return false;
     }
   }
 }
@@ -233,8 +251,9 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 // ---------------------------------------------------------------------------
 struct Barriers {
   uint64_t w_full[kMaxWStages], w_empty[kMaxWStages];
-  uint64_t a_full[kAStages], a_empty[kAStages];
-  uint64_t b_full[8], b_empty[8];
+  uint64_t a_full[kMaxAStages];    // dequant warps -> MMA issuer (4 arrivals, one per TMEM lane quarter)
+  uint64_t stage_done[kMaxAStages];  // MMA completion of a stage: frees its A slot AND its token slot
+  uint64_t b_full[kMaxBStages];
   uint64_t sc_full[2], sc_empty[2];
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
@@ -243,14 +262,38 @@ struct Barriers {
   float tile_w[kMaxTok];
 };
 
+// Ring position: slot index and phase parity, advanced without division.
+struct Ring {
+  int slot = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++slot == depth) {
+      slot = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <bool GATEUP>
+// KS = K elements per pipeline stage (one A slot in tensor memory, one token
+// slot in shared memory, one handshake of the MMA issuer). The issuer's
+// per-stage latency (barrier polls + commit) is a few hundred cycles whatever
+// the stage holds, so small token tiles, whose MMAs are short, take long
+// stages: KS = 64 for tiles up to 256 tokens, 128 up to 128, 256 up to 64.
+template <bool GATEUP, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
+  constexpr int kAccCols = KS == 64 ? 256 : (KS == 128 ? 128 : 64);   // accumulator columns
+  constexpr int kACols = KS / 2;                                      // columns of one A slot
+  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // 8, 6, 3
+  constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
+  constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
+  static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -267,14 +310,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->w_full[i]), 1);
       mbar_init(smem_u32(&bars->w_empty[i]), 8);
     }
-    for (int i = 0; i < kAStages; ++i) {
+    for (int i = 0; i < kMaxAStages; ++i) {
       mbar_init(smem_u32(&bars->a_full[i]), 4);
-      mbar_init(smem_u32(&bars->a_empty[i]), 1);
+      mbar_init(smem_u32(&bars->stage_done[i]), 1);
     }
-    for (int i = 0; i < 8; ++i) {
-      mbar_init(smem_u32(&bars->b_full[i]), 1);
-      mbar_init(smem_u32(&bars->b_empty[i]), 1);
-    }
+    for (int i = 0; i < kMaxBStages; ++i) mbar_init(smem_u32(&bars->b_full[i]), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->sc_full[i]), 1);
       mbar_init(smem_u32(&bars->sc_empty[i]), 8);
@@ -300,16 +340,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int n_tok_tiles = *p.n_tiles;
   const int n_items = n_tok_tiles * p.n_ftiles;
   const int n_kw = (p.K + kWStageK - 1) / kWStageK;   // packed-weight stages per item
-  const int n_sub_total = p.K / kSubK;                // A / token stages per item
+  const int n_stages = (p.K + KS - 1) / KS;           // pipeline stages per item (last may be short)
   const int pitch = p.K / 32;                         // scale bytes per weight row
   const int n_wrows = GATEUP ? 2 * p.n_feat : p.n_feat;
+  const int slice_bytes = p.max_tok * 128;            // one 64-K slice of a token stage
 
   if (warp == 0) {
     // ------------------- TMA producer: packed weights + scales ---------------
-    // Runs ahead of the token producer by the depth of its own ring, so the
-    // weight stream (the HBM-bound part) is never held back by token stages.
+    // Runs ahead by the depth of its own ring, independent of the token stages,
+    // so the weight stream (the HBM-bound part) is never held back by them.
     if (lane == 0) {
-      uint32_t w_it = 0, sc_it = 0;
+      Ring w;
+      uint32_t sc_it = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const TokTile tt = p.tiles[item / p.n_ftiles];
@@ -337,91 +379,116 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             bulk_load_1d(dst + half, p.w_scale + (size_t)row_b * pitch, half, bar);
           ++sc_it;
         }
-        for (int kw = 0; kw < n_kw; ++kw, ++w_it) {
-          const int s = w_it % p.w_stages;
-          const uint32_t par = ((w_it / p.w_stages) & 1u) ^ 1u;
-          if (!mbar_wait(smem_u32(&bars->w_empty[s]), par, abort_flag, 2)) { ok = false; break; }
-          const uint32_t bar = smem_u32(&bars->w_full[s]);
-          const uint32_t dst = smem_u32(w_smem + s * kWStageBytes);
+        for (int kw = 0; kw < n_kw; ++kw) {
+          if (!mbar_wait(smem_u32(&bars->w_empty[w.slot]), w.phase ^ 1u, abort_flag, 2)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&bars->w_full[w.slot]);
+          const uint32_t dst = smem_u32(w_smem + w.slot * kWStageBytes);
           mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
           tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
           if (rows_valid == 128)
             tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
+          w.advance(p.w_stages);
         }
       }
     }
   } else if (warp == 2) {
     // ------------------- TMA producer: token tiles ---------------------------
+    // Token slot of stage s is free once the MMAs of stage s - b_stages are done;
+    // that event is stage_done of the A slot that stage used (b_stages <= kAStages,
+    // so the barrier cannot have moved on to a later phase yet).
     if (lane == 0) {
-      uint32_t b_it = 0;
+      Ring b, lag;           // lag trails b by b_stages stages, on the A ring
+      int issued = 0;        // stages issued so far (all items)
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const TokTile tt = p.tiles[item / p.n_ftiles];
-        for (int sub = 0; sub < n_sub_total; ++sub, ++b_it) {
-          const int s = b_it % p.b_stages;
-          const uint32_t par = ((b_it / p.b_stages) & 1u) ^ 1u;
-          if (!mbar_wait(smem_u32(&bars->b_empty[s]), par, abort_flag, 3)) { ok = false; break; }
-          const uint32_t bar = smem_u32(&bars->b_full[s]);
-          const uint32_t dst = smem_u32(b_smem + s * p.b_stage_bytes);
-          mbar_expect_tx(bar, tt.n_rows * 128);
-          int r = 0;
-          for (; r + 64 <= tt.n_rows; r += 64)
-            tma_load_2d(dst + r * 128, &tmap_b64, sub * kSubK, tt.row0 + r, bar);
-          for (; r < tt.n_rows; r += 16)
-            tma_load_2d(dst + r * 128, &tmap_b, sub * kSubK, tt.row0 + r, bar);
+        for (int st = 0; st < n_stages; ++st, ++issued) {
+          if (issued >= p.b_stages) {
+            if (!mbar_wait(smem_u32(&bars->stage_done[lag.slot]), lag.phase, abort_flag, 3)) {
+              ok = false;
+              break;
+            }
+            lag.advance(kAStages);
+          }
+          const uint32_t bar = smem_u32(&bars->b_full[b.slot]);
+          const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
+          const int k0 = st * KS;
+          const int n_slices = min(kPieces, (p.K - k0) / 64);
+          mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
+          for (int sl = 0; sl < n_slices; ++sl) {
+            int r = 0;
+            for (; r + 64 <= tt.n_rows; r += 64)
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
+            for (; r < tt.n_rows; r += 16)
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
+          }
+          b.advance(p.b_stages);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer -----------------------------
-    if (lane == 0) {
-      uint32_t a_it = 0, b_it = 0, item_it = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
-        const TokTile tt = p.tiles[item / p.n_ftiles];
-        const uint32_t idesc = make_idesc(tt.n_rows);
-        if (!mbar_wait(smem_u32(&bars->acc_empty), (item_it & 1u) ^ 1u, abort_flag, 4)) break;
-        tc_fence_after();
-        bool ok = true;
-        for (int sub = 0; sub < n_sub_total; ++sub) {
-          const int sa = a_it % kAStages, sb = b_it % p.b_stages;
-          if (!mbar_wait(smem_u32(&bars->a_full[sa]), (a_it / kAStages) & 1u, abort_flag, 5) ||
-              !mbar_wait(smem_u32(&bars->b_full[sb]), (b_it / p.b_stages) & 1u, abort_flag, 6)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t b_addr = smem_u32(b_smem + sb * p.b_stage_bytes);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            tc_mma_ts(tmem_base, tmem_base + kAccCols + sa * 32 + kk * 8,
-                      make_b_desc(b_addr + kk * 32), idesc, (sub | kk) != 0 ? 1u : 0u);
-          }
-          tc_commit(smem_u32(&bars->a_empty[sa]));
-          tc_commit(smem_u32(&bars->b_empty[sb]));
-          ++a_it;
-          ++b_it;
+    // The whole warp stays converged: lanes 0 and 1 poll the A-ready and the
+    // tokens-ready barrier of the stage in the SAME instruction (one poll latency
+    // instead of two), lane 0 issues the MMAs and one commit per stage.
+    Ring a, b;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const TokTile tt = p.tiles[item / p.n_ftiles];
+      const uint32_t idesc = make_idesc(tt.n_rows);
+      if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
+      tc_fence_after();
+      for (int st = 0; st < n_stages; ++st) {
+        const uint32_t bar = lane == 0 ? smem_u32(&bars->a_full[a.slot]) : smem_u32(&bars->b_full[b.slot]);
+        const uint32_t par = lane == 0 ? a.phase : b.phase;
+        if (!mbar_wait_lanes(bar, par, lane < 2, abort_flag, 5)) {
+          ok = false;
+          break;
         }
-        if (!ok) break;
-        tc_commit(smem_u32(&bars->acc_full));
+        tc_fence_after();
+        if (lane == 0) {
+          const int n_slices = min(kPieces, (p.K - st * KS) / 64);
+          const uint32_t a_addr = tmem_base + kAccCols + a.slot * kACols;
+          const uint64_t desc0 = make_b_desc(smem_u32(b_smem + b.slot * p.b_stage_bytes));
+          const uint32_t slice16 = (uint32_t)slice_bytes >> 4;
+#pragma unroll
+          for (int sl = 0; sl < kPieces; ++sl) {
+            if (sl < n_slices) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                tc_mma_ts(tmem_base, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                          (st | sl | kk) != 0 ? 1u : 0u);
+            }
+          }
+          tc_commit(smem_u32(&bars->stage_done[a.slot]));
+          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
+        }
+        __syncwarp();
+        a.advance(kAStages);
+        b.advance(p.b_stages);
       }
+      acc_phase ^= 1u;
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------ dequant --------------------------------
-    // Warp (q, h): TMEM lane quarter q; of the 64-K A stages it takes those with
-    // stage counter % 2 == h, a full stage (32 columns) at a time. The tcgen05.st
-    // of one stage is left in flight while the next stage of this warp is
-    // decoded into the other register set; its completion is awaited, and the
-    // stage handed to the MMA warp, just before the next store.
+    // Warp (q, h): TMEM lane quarter q; it takes the stages whose running index
+    // has parity h. A stage is decoded 64 K-elements (32 columns) at a time:
+    // two 16-byte chunks of the thread's row -> 32 registers -> one tcgen05.st.
+    // With 64-K stages the store of a stage stays in flight while the warp's next
+    // stage is decoded; longer stages overlap their own pieces instead.
     const int q = warp & 3, h = (warp - 4) >> 2;
     const int row = q * 32 + lane;                 // TMEM lane of this thread
     // gate/up items interleave the two halves: even lanes hold gate rows, odd
     // lanes the matching up rows, so the epilogue pairs them with one shuffle.
     const int srow = GATEUP ? ((row & 1) * 64 + (row >> 1)) : row;   // row inside the staged tile
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols;
-    uint32_t w_it = 0, a_it = 0, sc_it = 0;
-    uint32_t va[32], vb[32];
-    int pending = -1;   // A stage whose store is still in flight
-    uint32_t flip = 0;
+    Ring w, a;
+    uint32_t sc_it = 0, stage_idx = 0;
+    int pending = -1;   // A slot whose stores are not yet handed to the MMA issuer
     bool ok = true;
     auto retire = [&]() {
       if (pending >= 0) {
@@ -442,50 +509,54 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
       const uint8_t* my_scales = sc_smem + sbuf * p.scale_buf_bytes + srow * pitch;
       for (int kw = 0; kw < n_kw && ok; ++kw) {
-        const int sw = w_it % p.w_stages;
-        if (!mbar_wait(smem_u32(&bars->w_full[sw]), (w_it / p.w_stages) & 1u, abort_flag, 8)) {
+        if (!mbar_wait(smem_u32(&bars->w_full[w.slot]), w.phase, abort_flag, 8)) {
           ok = false;
           break;
         }
-        const uint8_t* my_row = w_smem + sw * kWStageBytes + (srow >> 6) * (kWStageBytes / 2) +
+        const uint8_t* my_row = w_smem + w.slot * kWStageBytes + (srow >> 6) * (kWStageBytes / 2) +
                                 (srow & 63) * 128;
-        const int n_sub = min(4, n_sub_total - kw * 4);
-        for (int j = 0; j < n_sub; ++j, ++a_it) {
-          if ((a_it & 1u) != (uint32_t)h) continue;
-          const int sa = a_it % kAStages;
-          if (!mbar_wait(smem_u32(&bars->a_empty[sa]), ((a_it / kAStages) & 1u) ^ 1u, abort_flag,
-                         9)) {
+        const int k_left = p.K - kw * kWStageK;                       // K elements from this W stage on
+        const int n_sub = min(kSubPerW, (k_left + KS - 1) / KS);      // pipeline stages in this W stage
+        for (int j = 0; j < n_sub; ++j, ++stage_idx, a.advance(kAStages)) {
+          if ((stage_idx & 1u) != (uint32_t)h) continue;
+          if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 9)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          uint32_t* v = flip ? vb : va;
-          if (srow < rows_valid) {
-            const int c0 = j * 2;   // two 16-byte chunks = two scale groups of 32 K elements
-            const uint4 p0 = *reinterpret_cast<const uint4*>(my_row + (((c0) ^ (srow & 7)) << 4));
-            const uint4 p1 = *reinterpret_cast<const uint4*>(my_row + (((c0 + 1) ^ (srow & 7)) << 4));
-            const uint32_t s0 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0]);
-            const uint32_t s1 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0 + 1]);
-            dequant8(p0.x, s0, v + 0);
-            dequant8(p0.y, s0, v + 4);
-            dequant8(p0.z, s0, v + 8);
-            dequant8(p0.w, s0, v + 12);
-            dequant8(p1.x, s1, v + 16);
-            dequant8(p1.y, s1, v + 20);
-            dequant8(p1.z, s1, v + 24);
-            dequant8(p1.w, s1, v + 28);
-          } else {
+          const int n_pieces = min(kPieces, (k_left - j * KS) / 64);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          for (int pc = 0; pc < kPieces; ++pc) {
+            if (pc < n_pieces) {
+              uint32_t v[32];
+              if (srow < rows_valid) {
+                const int c0 = (j * kPieces + pc) * 2;   // two 16-byte chunks = two scale groups
+                const uint4 p0 = *reinterpret_cast<const uint4*>(my_row + (((c0) ^ (srow & 7)) << 4));
+                const uint4 p1 = *reinterpret_cast<const uint4*>(my_row + (((c0 + 1) ^ (srow & 7)) << 4));
+                const uint32_t s0 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0]);
+                const uint32_t s1 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0 + 1]);
+                dequant8(p0.x, s0, v + 0);
+                dequant8(p0.y, s0, v + 4);
+                dequant8(p0.z, s0, v + 8);
+                dequant8(p0.w, s0, v + 12);
+                dequant8(p1.x, s1, v + 16);
+                dequant8(p1.y, s1, v + 20);
+                dequant8(p1.z, s1, v + 24);
+                dequant8(p1.w, s1, v + 28);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0u;
+              }
+              if (KS == 64) retire();   // previous stage of this warp: its store had a stage time to land
+              tc_st32(t_row + a.slot * kACols + pc * 32, v);
+            }
           }
-          retire();
-          tc_st32(t_row + sa * 32, v);
-          pending = sa;
-          flip ^= 1u;
+          pending = a.slot;
+          if (KS != 64) retire();
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->w_empty[sw]));
-        ++w_it;
+        if (lane == 0) mbar_arrive(smem_u32(&bars->w_empty[w.slot]));
+        w.advance(p.w_stages);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->sc_empty[sbuf]));
@@ -496,8 +567,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // ------------------------------ epilogue -------------------------------
     const int q = warp & 3;
     const int etid = tid - 12 * 32;  // 0..127 = TMEM lane
-    uint32_t item_it = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, acc_phase ^= 1u) {
       const TokTile tt = p.tiles[item / p.n_ftiles];
       const int f = item % p.n_ftiles;
       // per-token info of this item (previous item's readers are past the barrier below)
@@ -509,7 +580,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
       named_bar_sync(1, 128);
-      if (!mbar_wait(smem_u32(&bars->acc_full), item_it & 1u, abort_flag, 10)) break;
+      if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10)) break;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       if (GATEUP) {
@@ -545,9 +616,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
       } else {
         const int rows_valid = min(128, p.n_feat - f * 128);
-        const int h = f * 128 + etid;
+        const int hcol = f * 128 + etid;
         const bool row_ok = etid < rows_valid;
-        const float b = (p.bias && row_ok) ? p.bias[(size_t)tt.expert * p.n_feat + h] : 0.0f;
+        const float b = (p.bias && row_ok) ? p.bias[(size_t)tt.expert * p.n_feat + hcol] : 0.0f;
         for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
           uint32_t v[32];
           tc_ld32(t_lane + c0, v);
@@ -565,7 +636,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const int token = bars->tile_tok[t];
                 if (token >= 0) {
                   const float val = (__uint_as_float(v[j]) + b) * bars->tile_w[t];
-                  atomicAdd(p.out + (size_t)token * p.n_feat + h, val);
+                  atomicAdd(p.out + (size_t)token * p.n_feat + hcol, val);
                 }
               }
             }
@@ -748,39 +819,53 @@ int sm_count() {
   return n;
 }
 
-template <bool GATEUP>
-void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
-                 cudaStream_t stream) {
-  // Shared memory: token stages of max_tok rows, scales (double-buffered when they fit), barriers;
-  // what is left becomes the packed-weight ring (3..8 stages of 16 KB): the deeper it is, the more
-  // weight bytes are in flight, which is what a decode-size batch is bound by.
+template <bool GATEUP, int KS>
+void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
+                    cudaStream_t stream) {
+  // Shared memory: token stages (max_tok rows x KS), scales (double-buffered when they fit),
+  // barriers; what is left becomes the packed-weight ring (3..8 stages of 16 KB): the deeper it
+  // is, the more weight bytes are in flight, which is what a decode-size batch is bound by.
+  constexpr int kAccCols = KS == 64 ? 256 : (KS == 128 ? 128 : 64);
+  constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (int)sizeof(Barriers) + 256;
-  p.b_stage_bytes = p.max_tok * 128;
-  int b_stages = 4, scale_bufs = 2;
-  auto w_room = [&]() { return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes; };
+  p.b_stage_bytes = p.max_tok * 128 * (KS / 64);
+  int b_stages = kAStages < 4 ? kAStages : 4, scale_bufs = 2;
+  auto w_room = [&]() {
+    return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
+  };
   if (w_room() < 4) scale_bufs = 1;
-  if (w_room() < 3) b_stages = 3;
-  if (w_room() < 3) b_stages = 2;
+  if (w_room() < 3 && b_stages > 3) b_stages = 3;
+  if (w_room() < 3 && b_stages > 2) b_stages = 2;
   expects(w_room() >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
   p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
   if (p.w_stages == kMaxWStages) {   // spare room: deepen the token ring too
-    while (b_stages < 8 && (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) /
-                                   kWStageBytes >= kMaxWStages)
+    while (b_stages < kAStages && b_stages < kMaxBStages &&
+           (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWStageBytes >=
+               kMaxWStages)
       ++b_stages;
   }
   p.b_stages = b_stages;
   p.scale_bufs = scale_bufs;
   p.scale_buf_bytes = scale_tile;
   const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWStageBytes;
-  static bool configured[2] = {false, false};
-  if (!configured[GATEUP]) {
-    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP>,
+  static bool configured = false;
+  if (!configured) {
+    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    configured[GATEUP] = true;
+    configured = true;
   }
-  moe_gemm_sm100_kernel<GATEUP><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+  moe_gemm_sm100_kernel<GATEUP, KS><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+}
+
+// Stage length by the largest token tile of the launch (see the kernel's comment).
+template <bool GATEUP>
+void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
+                 cudaStream_t stream) {
+  if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256>(tw, tb, tb64, p, stream);
+  else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128>(tw, tb, tb64, p, stream);
+  else launch_gemm_ks<GATEUP, 64>(tw, tb, tb64, p, stream);
 }
 
 }  // namespace
