@@ -225,6 +225,37 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// One lane of a fully converged warp, chosen by the hardware: code guarded by
+// it is known to the compiler to run in a single thread, which lets it keep
+// the MMA operands in uniform registers instead of serialising over lanes.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xFFFFFFFF;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+// Gate/up activation with the hardware exp / reciprocal approximations (relative
+// error ~1e-6, far inside the layer's tolerance; the CUDA-core cross-check path
+// keeps the accurate functions). SiTU and non-finite gates take the accurate
+// functions so inf / NaN propagate exactly as in the CPU definition.
+__device__ __forceinline__ float moe_act_fast(int activation, float g, float u, float limit, float beta,
+                                              float linear_beta) {
+  if (activation == 1 || !(fabsf(g) < INFINITY))
+    return moe_act_value(activation, g, u, limit, beta, linear_beta);
+  if (limit > 0.0f) {
+    g = (g > limit) ? limit : g;
+    u = (u > limit) ? limit : u;
+    u = (u < -limit) ? -limit : u;
+  }
+  // exp(-g) overflows fp32 beyond 88; the quotient is then below 1e-36 in magnitude either way.
+  const float ng = (-g > 87.0f) ? 87.0f : -g;
+  return __fdividef(g, 1.0f + __expf(ng)) * u;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int n) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
@@ -437,9 +468,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     Ring a, b;
     uint32_t acc_phase = 0;
     bool ok = true;
+    const uint32_t tmem_u = __shfl_sync(0xFFFFFFFFu, tmem_base, 0);
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const TokTile tt = p.tiles[item / p.n_ftiles];
-      const uint32_t idesc = make_idesc(tt.n_rows);
+      const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / p.n_ftiles].n_rows, 0);
+      const uint32_t idesc = make_idesc(n_rows_u);
       if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
       tc_fence_after();
       for (int st = 0; st < n_stages; ++st) {
@@ -450,9 +482,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           break;
         }
         tc_fence_after();
-        if (lane == 0) {
+        if (elect_one()) {
           const int n_slices = min(kPieces, (p.K - st * KS) / 64);
-          const uint32_t a_addr = tmem_base + kAccCols + a.slot * kACols;
+          const uint32_t a_addr = tmem_u + kAccCols + a.slot * kACols;
           const uint64_t desc0 = make_b_desc(smem_u32(b_smem + b.slot * p.b_stage_bytes));
           const uint32_t slice16 = (uint32_t)slice_bytes >> 4;
 #pragma unroll
@@ -460,7 +492,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (sl < n_slices) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                tc_mma_ts(tmem_base, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
                           (st | sl | kk) != 0 ? 1u : 0u);
             }
           }
@@ -600,7 +632,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
           }
-          const int tbase = c0 + (odd ? 16 : 0);
+          // which of the round's 32 tokens are real rows: one shared-memory read per lane and
+          // a ballot, so the 16 stores below depend on no load
+          const int my_t = c0 + lane;
+          const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_tok[my_t] >= 0);
+          const int tsel = odd ? 16 : 0;
+          uint16_t* dst = p.act + (size_t)(tt.row0 + c0 + tsel) * p.n_feat + feat;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const uint32_t mine = odd ? v[16 + j] : v[j];      // my row, my tokens
@@ -608,10 +645,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, give, 1);
             const float g = __uint_as_float(odd ? got : mine) + bg;
             const float u = __uint_as_float(odd ? mine : got) + bu;
-            const int t = tbase + j;
-            if (t < tt.n_rows && bars->tile_tok[t] >= 0)
-              p.act[(size_t)(tt.row0 + t) * p.n_feat + feat] =
-                  f32_to_bf16_bits(moe_act_value(p.activation, g, u, p.limit, p.beta, p.linear_beta));
+            if ((real >> (tsel + j)) & 1u)
+              dst[(size_t)j * p.n_feat] =
+                  f32_to_bf16_bits(moe_act_fast(p.activation, g, u, p.limit, p.beta, p.linear_beta));
           }
         }
       } else {
@@ -628,18 +664,17 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
           }
-          if (row_ok) {
+          // lane l keeps token and routing weight of column c0 + l; the loop broadcasts them by
+          // shuffle, so no reduction below waits on a shared-memory load
+          const int my_t = c0 + lane;
+          const int my_tok = my_t < tt.n_rows ? bars->tile_tok[my_t] : -1;
+          const float my_w = my_t < tt.n_rows ? bars->tile_w[my_t] : 0.0f;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int t = c0 + j;
-              if (t < tt.n_rows) {
-                const int token = bars->tile_tok[t];
-                if (token >= 0) {
-                  const float val = (__uint_as_float(v[j]) + b) * bars->tile_w[t];
-                  atomicAdd(p.out + (size_t)token * p.n_feat + hcol, val);
-                }
-              }
-            }
+          for (int j = 0; j < 32; ++j) {
+            const int token = __shfl_sync(0xFFFFFFFFu, my_tok, j);
+            const float wgt = __shfl_sync(0xFFFFFFFFu, my_w, j);
+            if (token >= 0 && row_ok)
+              atomicAdd(p.out + (size_t)token * p.n_feat + hcol, (__uint_as_float(v[j]) + b) * wgt);
           }
         }
       }

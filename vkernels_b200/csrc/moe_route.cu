@@ -71,6 +71,31 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
   }
 }
 
+// Small batches: one warp per (token, expert) dot product, 128-bit loads, so a decode
+// step fills the machine instead of running on a couple of CTAs.
+__global__ void __launch_bounds__(256)
+router_logits_warp_kernel(const uint16_t* __restrict__ x, const float* __restrict__ wr,
+                          float* __restrict__ logits, int T, int H, int E) {
+  const int lane = threadIdx.x & 31;
+  const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= (long long)T * E) return;
+  const int t = (int)(pair / E), e = (int)(pair % E);
+  const uint2* xr = reinterpret_cast<const uint2*>(x + (size_t)t * H);     // 4 bf16
+  const float4* w = reinterpret_cast<const float4*>(wr + (size_t)e * H);   // 4 fp32
+  float acc = 0.0f;
+  for (int i = lane; i < H / 4; i += 32) {
+    const uint2 xv = xr[i];
+    const float4 wv = w[i];
+    acc = fmaf(bf16_bits_to_f32(xv.x & 0xFFFFu), wv.x, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.x >> 16), wv.y, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.y & 0xFFFFu), wv.z, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.y >> 16), wv.w, acc);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
+  if (lane == 0) logits[(size_t)t * E + e] = acc;
+}
+
 // ----------------------------- top-k ----------------------------------------
 // One warp per token. Expert e lives in lane e % 32, slot e / 32.
 constexpr int kMaxSlots = 32;  // E <= 1024
@@ -235,8 +260,14 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
   expects(T >= 0 && H > 0 && E > 0, "router_logits: bad dimensions");
   if (T == 0) return;
   expects(x && wr && logits, "router_logits: null buffer");
-  dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
-  router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, T, H, E);
+  if (T <= 512 && H % 4 == 0) {
+    const long long pairs = (long long)T * E;
+    router_logits_warp_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, wr, logits, T, H, E);
+  } else {
+    dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
+    router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, T, H, E);
+  }
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
