@@ -58,6 +58,7 @@ constexpr int kMaxBStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kThreads = 512;
 constexpr int kTmemCols = 512;
+constexpr int kEpiStageBytes = 2 * 32 * 64 * 2;   // gate/up epilogue staging (two rounds)
 constexpr uint32_t kSpinLimit = 40u * 1000u * 1000u;
 
 struct TokTile {
@@ -239,22 +240,23 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
-// Gate/up activation with the hardware exp / reciprocal approximations (relative
-// error ~1e-6, far inside the layer's tolerance; the CUDA-core cross-check path
-// keeps the accurate functions). SiTU and non-finite gates take the accurate
-// functions so inf / NaN propagate exactly as in the CPU definition.
-__device__ __forceinline__ float moe_act_fast(int activation, float g, float u, float limit, float beta,
-                                              float linear_beta) {
-  if (activation == 1 || !(fabsf(g) < INFINITY))
-    return moe_act_value(activation, g, u, limit, beta, linear_beta);
-  if (limit > 0.0f) {
+// SwiGLU with the hardware exp / reciprocal approximations (relative error
+// ~1e-6, far inside the layer's tolerance; the CUDA-core cross-check path keeps
+// the accurate functions). Straight-line code - no data-dependent branch - so
+// the 16 elements a thread finishes per round overlap their latencies. inf and
+// NaN come out as in the CPU definition: NaN stays NaN (comparisons with NaN
+// are false), +inf gives inf * u, and -inf, where the definition evaluates
+// -inf / inf = NaN, is patched by the final select.
+__device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
+  if (limit > 0.0f) {   // uniform across the launch
     g = (g > limit) ? limit : g;
     u = (u > limit) ? limit : u;
     u = (u < -limit) ? -limit : u;
   }
-  // exp(-g) overflows fp32 beyond 88; the quotient is then below 1e-36 in magnitude either way.
+  // exp(-g) overflows fp32 beyond 88; the quotient is below 1e-36 in magnitude either way.
   const float ng = (-g > 87.0f) ? 87.0f : -g;
-  return __fdividef(g, 1.0f + __expf(ng)) * u;
+  const float r = __fdividef(g, 1.0f + __expf(ng));
+  return ((g == -INFINITY) ? __int_as_float(0x7FC00000) : r) * u;
 }
 __device__ __forceinline__ void named_bar_sync(int id, int n) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
@@ -332,6 +334,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint8_t* b_smem = w_smem + p.w_stages * kWStageBytes;        // b_stages x b_stage_bytes
   uint8_t* sc_smem = b_smem + p.b_stages * p.b_stage_bytes;    // scale_bufs x scale_buf_bytes
   Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
+  // gate/up epilogue staging: 2 x (32 tokens x 64 features) bf16, 16-byte aligned
+  uint16_t* epi_stage = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(Barriers) + 127) & ~size_t(127)));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
@@ -600,6 +604,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int q = warp & 3;
     const int etid = tid - 12 * 32;  // 0..127 = TMEM lane
     uint32_t acc_phase = 0;
+    int round = 0;   // gate/up staging buffer parity, running over all items
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, acc_phase ^= 1u) {
       const TokTile tt = p.tiles[item / p.n_ftiles];
       const int f = item % p.n_ftiles;
@@ -620,10 +625,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         // dequant role). Per 32 columns the pair exchanges halves with one shuffle
         // each: the even lane finishes tokens 0..15, the odd lane tokens 16..31.
         const bool odd = lane & 1;
+        const bool situ = p.activation == 1;   // uniform across the launch
         const int feat = f * 64 + q * 16 + (lane >> 1);
         const float bg = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + feat] : 0.0f;
         const float bu = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + p.n_feat + feat] : 0.0f;
-        for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+        for (int c0 = 0; c0 < tt.n_rows; c0 += 32, ++round) {
           uint32_t v[32];
           tc_ld32(t_lane + c0, v);
           tc_wait_ld();
@@ -637,17 +643,38 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const int my_t = c0 + lane;
           const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_tok[my_t] >= 0);
           const int tsel = odd ? 16 : 0;
-          uint16_t* dst = p.act + (size_t)(tt.row0 + c0 + tsel) * p.n_feat + feat;
+          // the exchange: 16 shuffles, then g/u of this thread's 16 tokens in registers
+          float gv[16], uv[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const uint32_t mine = odd ? v[16 + j] : v[j];      // my row, my tokens
             const uint32_t give = odd ? v[j] : v[16 + j];      // my row, partner's tokens
             const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, give, 1);
-            const float g = __uint_as_float(odd ? got : mine) + bg;
-            const float u = __uint_as_float(odd ? mine : got) + bu;
-            if ((real >> (tsel + j)) & 1u)
-              dst[(size_t)j * p.n_feat] =
-                  f32_to_bf16_bits(moe_act_fast(p.activation, g, u, p.limit, p.beta, p.linear_beta));
+            gv[j] = __uint_as_float(odd ? got : mine) + bg;
+            uv[j] = __uint_as_float(odd ? mine : got) + bu;
+          }
+          // activation -> bf16 into the staging tile [token][feature] of this round ...
+          uint16_t* stg = epi_stage + (round & 1) * (32 * 64) + tsel * 64 + (q * 16 + (lane >> 1));
+          if (!situ) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stg[j * 64] = f32_to_bf16_bits(swiglu_fast(gv[j], uv[j], p.limit));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              stg[j * 64] = f32_to_bf16_bits(moe_act_value(1, gv[j], uv[j], p.limit, p.beta, p.linear_beta));
+          }
+          // ... then rows leave as 16-byte pieces: 8 consecutive threads write one 128-byte act row.
+          // One barrier per round: a buffer is rewritten two rounds later, after the barrier of
+          // the round in between, which every reader of this round has passed by then.
+          named_bar_sync(2, 128);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int piece = etid + i * 128;           // 256 pieces of 16 bytes
+            const int tok = piece >> 3, ch = piece & 7;
+            if ((real >> tok) & 1u) {
+              const uint4 val = *reinterpret_cast<const uint4*>(epi_stage + (round & 1) * (32 * 64) + tok * 64 + ch * 8);
+              *reinterpret_cast<uint4*>(p.act + (size_t)(tt.row0 + c0 + tok) * p.n_feat + f * 64 + ch * 8) = val;
+            }
           }
         }
       } else {
@@ -864,7 +891,7 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
-  const int fixed = 1024 + (int)sizeof(Barriers) + 256;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : 0) + 128;
   p.b_stage_bytes = p.max_tok * 128 * (KS / 64);
   int b_stages = kAStages < 4 ? kAStages : 4, scale_bufs = 2;
   auto w_room = [&]() {
