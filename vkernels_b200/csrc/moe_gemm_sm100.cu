@@ -35,6 +35,7 @@
 // (moe_fused.hip:1448-1663).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -51,7 +52,6 @@ namespace {
 constexpr int kMaxTok = 256;        // tokens (MMA N) per work item
 constexpr int kRows = 128;          // weight rows (MMA M) per work item
 constexpr int kWStageK = 256;       // K elements per packed-weight stage (128 B per row)
-constexpr int kSubK = 64;           // K elements per A stage / token stage (128 B of bf16)
 constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per launch (3..8)
 constexpr int kMaxAStages = 8;
 constexpr int kMaxBStages = 8;
@@ -59,7 +59,7 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kThreads = 512;
 constexpr int kTmemCols = 512;
 constexpr int kEpiStageBytes = 2 * 32 * 64 * 2;   // gate/up epilogue staging (two rounds)
-constexpr uint32_t kSpinLimit = 40u * 1000u * 1000u;
+constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
 
 struct TokTile {
   int expert;
@@ -258,6 +258,58 @@ __device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
   const float r = __fdividef(g, 1.0f + __expf(ng));
   return ((g == -INFINITY) ? __int_as_float(0x7FC00000) : r) * u;
 }
+// ---- CTA-pair (cta_group::2) helpers ---------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.
+// CTA-scope release (the default): the arrival only hands over tensor-memory contents, which
+// the tcgen05 fences order; a cluster-scope release costs over a thousand cycles per arrival.
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar, uint32_t cta) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(bar),
+      "r"(cta)
+      : "memory");
+}
+// Token-tile load of a CTA pair: the data lands in THIS CTA's shared memory, the
+// transaction bytes are credited to the barrier at the same offset in the pair's
+// leader (even) CTA, whose MMA thread consumes both halves. No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar & 0xFEFFFFFFu)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+          "r"(bar),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int n) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
@@ -275,8 +327,8 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------
@@ -315,7 +367,7 @@ struct Ring {
 // per-stage latency (barrier polls + commit) is a few hundred cycles whatever
 // the stage holds, so small token tiles, whose MMAs are short, take long
 // stages: KS = 64 for tiles up to 256 tokens, 128 up to 128, 256 up to 64.
-template <bool GATEUP, int KS>
+template <bool GATEUP, int KS, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
@@ -326,6 +378,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
   constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
   static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
+  static_assert(CTAS == 1 || KS == 64, "the CTA-pair form is built for 64-K stages");
+  // CTAS == 2: two CTAs of a cluster work on one item - 256 weight rows (128 per CTA, each CTA
+  // dequantises its own) against ONE token tile of up to 256 tokens, of which each CTA stages only
+  // half. The leader (even) CTA issues cta_group::2 MMAs that read both halves; every CTA keeps
+  // its 128 accumulator rows in its own tensor memory. This halves the token bytes a CTA pulls
+  // from L2 per flop and doubles the depth of the token ring that fits in shared memory.
+  const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -346,7 +406,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->w_empty[i]), 8);
     }
     for (int i = 0; i < kMaxAStages; ++i) {
-      mbar_init(smem_u32(&bars->a_full[i]), 4);
+      mbar_init(smem_u32(&bars->a_full[i]), 4 * CTAS);
       mbar_init(smem_u32(&bars->stage_done[i]), 1);
     }
     for (int i = 0; i < kMaxBStages; ++i) mbar_init(smem_u32(&bars->b_full[i]), 1);
@@ -355,30 +415,44 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->sc_empty[i]), 8);
     }
     mbar_init(smem_u32(&bars->acc_full), 1);
-    mbar_init(smem_u32(&bars->acc_empty), 4);
+    mbar_init(smem_u32(&bars->acc_empty), 4 * CTAS);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&bars->tmem_base)),
-                 "r"((uint32_t)kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&bars->tmem_base)),
+                   "r"((uint32_t)kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&bars->tmem_base)),
+                   "r"((uint32_t)kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
   const int n_tok_tiles = *p.n_tiles;
-  const int n_items = n_tok_tiles * p.n_ftiles;
+  const int unit = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // CTA (pair) index
+  const int n_units = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int n_fgroups = (p.n_ftiles + CTAS - 1) / CTAS;   // feature tiles per token tile, in units of CTAS
+  const int n_items = n_tok_tiles * n_fgroups;
+  // feature tile of this CTA inside an item; with an odd tile count the last pair's second CTA idles
+  auto item_f = [&](int item) { return (item % n_fgroups) * CTAS + (int)cta_rank; };
   const int n_kw = (p.K + kWStageK - 1) / kWStageK;   // packed-weight stages per item
   const int n_stages = (p.K + KS - 1) / KS;           // pipeline stages per item (last may be short)
   const int pitch = p.K / 32;                         // scale bytes per weight row
   const int n_wrows = GATEUP ? 2 * p.n_feat : p.n_feat;
-  const int slice_bytes = p.max_tok * 128;            // one 64-K slice of a token stage
+  const int slice_bytes = (p.max_tok / CTAS) * 128;   // one 64-K slice of a token stage (this CTA's rows)
 
   if (warp == 0) {
     // ------------------- TMA producer: packed weights + scales ---------------
@@ -388,9 +462,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       Ring w;
       uint32_t sc_it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const TokTile tt = p.tiles[item / p.n_ftiles];
-        const int f = item % p.n_ftiles;
+      for (int item = unit; item < n_items && ok; item += n_units) {
+        const TokTile tt = p.tiles[item / n_fgroups];
+        const int f = item_f(item);
         int row_a, row_b, rows_valid;   // two boxes of 64 weight rows
         if (GATEUP) {
           row_a = tt.expert * n_wrows + f * 64;
@@ -401,6 +475,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           row_b = row_a + 64;
           rows_valid = min(128, p.n_feat - f * 128);
         }
+        if (f >= p.n_ftiles) rows_valid = 0;   // idle half of the last pair: nothing to load
         {
           const int sb = sc_it % p.scale_bufs;
           const uint32_t par = ((sc_it / p.scale_bufs) & 1u) ^ 1u;
@@ -408,10 +483,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t bar = smem_u32(&bars->sc_full[sb]);
           const uint32_t dst = smem_u32(sc_smem + sb * p.scale_buf_bytes);
           const uint32_t half = 64u * pitch;
-          mbar_expect_tx(bar, rows_valid == 128 ? 2 * half : half);
-          bulk_load_1d(dst, p.w_scale + (size_t)row_a * pitch, half, bar);
-          if (rows_valid == 128)
-            bulk_load_1d(dst + half, p.w_scale + (size_t)row_b * pitch, half, bar);
+          if (rows_valid == 0) {
+            mbar_arrive(bar);
+          } else {
+            mbar_expect_tx(bar, rows_valid == 128 ? 2 * half : half);
+            bulk_load_1d(dst, p.w_scale + (size_t)row_a * pitch, half, bar);
+            if (rows_valid == 128)
+              bulk_load_1d(dst + half, p.w_scale + (size_t)row_b * pitch, half, bar);
+          }
           ++sc_it;
         }
         for (int kw = 0; kw < n_kw; ++kw) {
@@ -421,10 +500,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           }
           const uint32_t bar = smem_u32(&bars->w_full[w.slot]);
           const uint32_t dst = smem_u32(w_smem + w.slot * kWStageBytes);
-          mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
-          tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
-          if (rows_valid == 128)
-            tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
+          if (rows_valid == 0) {
+            mbar_arrive(bar);
+          } else {
+            mbar_expect_tx(bar, rows_valid == 128 ? kWStageBytes : kWStageBytes / 2);
+            tma_load_2d(dst, &tmap_w, kw * (kWStageK / 2), row_a, bar);
+            if (rows_valid == 128)
+              tma_load_2d(dst + kWStageBytes / 2, &tmap_w, kw * (kWStageK / 2), row_b, bar);
+          }
           w.advance(p.w_stages);
         }
       }
@@ -438,8 +521,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       Ring b, lag;           // lag trails b by b_stages stages, on the A ring
       int issued = 0;        // stages issued so far (all items)
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const TokTile tt = p.tiles[item / p.n_ftiles];
+      for (int item = unit; item < n_items && ok; item += n_units) {
+        const TokTile tt = p.tiles[item / n_fgroups];
         for (int st = 0; st < n_stages; ++st, ++issued) {
           if (issued >= p.b_stages) {
             if (!mbar_wait(smem_u32(&bars->stage_done[lag.slot]), lag.phase, abort_flag, 3)) {
@@ -452,13 +535,24 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
           const int k0 = st * KS;
           const int n_slices = min(kPieces, (p.K - k0) / 64);
-          mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
-          for (int sl = 0; sl < n_slices; ++sl) {
+          if (CTAS == 2) {
+            // MMA N = rows rounded up to 32; this CTA stages half of them. Rows past the tile are
+            // someone else's (or zero fill past the tensor): their columns are never read back.
+            const int half_rows = ((tt.n_rows + 31) >> 5) << 4;
+            const int my_row0 = tt.row0 + (int)cta_rank * half_rows;
+            if (leader) mbar_expect_tx(bar, 2 * half_rows * 128);
             int r = 0;
-            for (; r + 64 <= tt.n_rows; r += 64)
-              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
-            for (; r < tt.n_rows; r += 16)
-              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
+            for (; r + 64 <= half_rows; r += 64) tma_load_2d_pair(dst + r * 128, &tmap_b64, k0, my_row0 + r, bar);
+            for (; r < half_rows; r += 16) tma_load_2d_pair(dst + r * 128, &tmap_b, k0, my_row0 + r, bar);
+          } else {
+            mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
+            for (int sl = 0; sl < n_slices; ++sl) {
+              int r = 0;
+              for (; r + 64 <= tt.n_rows; r += 64)
+                tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
+              for (; r < tt.n_rows; r += 16)
+                tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
+            }
           }
           b.advance(p.b_stages);
         }
@@ -473,9 +567,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t tmem_u = __shfl_sync(0xFFFFFFFFu, tmem_base, 0);
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / p.n_ftiles].n_rows, 0);
-      const uint32_t idesc = make_idesc(n_rows_u);
+    for (int item = unit; item < n_items && ok && leader; item += n_units) {
+      const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
+      const uint32_t idesc = CTAS == 2 ? make_idesc((n_rows_u + 31) & ~31, 256) : make_idesc(n_rows_u);
       if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
       tc_fence_after();
       for (int st = 0; st < n_stages; ++st) {
@@ -496,12 +590,21 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (sl < n_slices) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
-                          (st | sl | kk) != 0 ? 1u : 0u);
+                if (CTAS == 2)
+                  tc_mma_ts_pair(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                                 (st | sl | kk) != 0 ? 1u : 0u);
+                else
+                  tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                            (st | sl | kk) != 0 ? 1u : 0u);
             }
           }
-          tc_commit(smem_u32(&bars->stage_done[a.slot]));
-          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
+          if (CTAS == 2) {   // completion is announced in both CTAs of the pair
+            tc_commit_pair(smem_u32(&bars->stage_done[a.slot]));
+            if (st == n_stages - 1) tc_commit_pair(smem_u32(&bars->acc_full));
+          } else {
+            tc_commit(smem_u32(&bars->stage_done[a.slot]));
+            if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
+          }
         }
         __syncwarp();
         a.advance(kAStages);
@@ -531,13 +634,16 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[pending]));
+        if (lane == 0) {
+          if (CTAS == 2 && !leader) mbar_arrive_cta(smem_u32(&bars->a_full[pending]), 0);
+          else mbar_arrive(smem_u32(&bars->a_full[pending]));
+        }
         pending = -1;
       }
     };
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const int f = item % p.n_ftiles;
-      const int rows_valid = GATEUP ? 128 : min(128, p.n_feat - f * 128);
+    for (int item = unit; item < n_items && ok; item += n_units) {
+      const int f = item_f(item);
+      const int rows_valid = f >= p.n_ftiles ? 0 : (GATEUP ? 128 : min(128, p.n_feat - f * 128));
       const int sbuf = sc_it % p.scale_bufs;
       if (!mbar_wait(smem_u32(&bars->sc_full[sbuf]), (sc_it / p.scale_bufs) & 1u, abort_flag, 7)) {
         ok = false;
@@ -605,9 +711,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int etid = tid - 12 * 32;  // 0..127 = TMEM lane
     uint32_t acc_phase = 0;
     int round = 0;   // gate/up staging buffer parity, running over all items
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, acc_phase ^= 1u) {
-      const TokTile tt = p.tiles[item / p.n_ftiles];
-      const int f = item % p.n_ftiles;
+    for (int item = unit; item < n_items; item += n_units, acc_phase ^= 1u) {
+      const TokTile tt = p.tiles[item / n_fgroups];
+      const int f = item_f(item);
       // per-token info of this item (previous item's readers are past the barrier below)
       named_bar_sync(1, 128);
       for (int j = etid; j < tt.n_rows; j += 128) {
@@ -620,6 +726,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10)) break;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2 && !leader) mbar_arrive_cta(smem_u32(&bars->acc_empty), 0);
+          else mbar_arrive(smem_u32(&bars->acc_empty));
+        }
+      };
+      if (f >= p.n_ftiles) {   // idle half of the last pair
+        release_acc();
+        continue;
+      }
       if (GATEUP) {
         // lane 2i holds the gate row, lane 2i+1 the up row of feature i (see the
         // dequant role). Per 32 columns the pair exchanges halves with one shuffle
@@ -633,11 +751,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           uint32_t v[32];
           tc_ld32(t_lane + c0, v);
           tc_wait_ld();
-          if (c0 + 32 >= tt.n_rows) {  // last read of the accumulator
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
-          }
+          if (c0 + 32 >= tt.n_rows) release_acc();   // last read of the accumulator
           // which of the round's 32 tokens are real rows: one shared-memory read per lane and
           // a ballot, so the 16 stores below depend on no load
           const int my_t = c0 + lane;
@@ -686,11 +800,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           uint32_t v[32];
           tc_ld32(t_lane + c0, v);
           tc_wait_ld();
-          if (c0 + 32 >= tt.n_rows) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
-          }
+          if (c0 + 32 >= tt.n_rows) release_acc();
           // lane l keeps token and routing weight of column c0 + l; the loop broadcasts them by
           // shuffle, so no reduction below waits on a shared-memory load
           const int my_t = c0 + lane;
@@ -711,11 +821,17 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // ------------------------------ teardown ---------------------------------
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();   // the peer no longer touches this CTA's barriers or tensor memory
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)kTmemCols)
-                 : "memory");
+    if (CTAS == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((uint32_t)kTmemCols)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((uint32_t)kTmemCols)
+                   : "memory");
   }
   if (tid == 0 && bars->abort_flag != 0) atomicExch(p.status, 100 + bars->abort_flag);
 }
@@ -881,32 +997,43 @@ int sm_count() {
   return n;
 }
 
-template <bool GATEUP, int KS>
+// Large token tiles run on CTA pairs; VK_MOE_PAIR=0 keeps every launch on single CTAs.
+bool pair_mode() {
+  static const bool on = [] {
+    const char* e = std::getenv("VK_MOE_PAIR");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return on;
+}
+
+template <bool GATEUP, int KS, int CTAS>
 void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                     cudaStream_t stream) {
-  // Shared memory: token stages (max_tok rows x KS), scales (double-buffered when they fit),
-  // barriers; what is left becomes the packed-weight ring (3..8 stages of 16 KB): the deeper it
-  // is, the more weight bytes are in flight, which is what a decode-size batch is bound by.
+  // Shared memory: token stages (this CTA's rows x KS), scales (double-buffered when they fit),
+  // barriers, epilogue staging; what is left becomes the packed-weight ring (3..8 stages of
+  // 16 KB): the deeper it is, the more weight bytes are in flight, which is what a decode-size
+  // batch is bound by.
   constexpr int kAccCols = KS == 64 ? 256 : (KS == 128 ? 128 : 64);
   constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : 0) + 128;
-  p.b_stage_bytes = p.max_tok * 128 * (KS / 64);
-  int b_stages = kAStages < 4 ? kAStages : 4, scale_bufs = 2;
+  p.b_stage_bytes = (p.max_tok / CTAS) * 128 * (KS / 64);
+  // token ring: 4 slots for a lone CTA; a pair stages half the rows per CTA and takes 6
+  int b_stages = CTAS == 2 ? 6 : (kAStages < 4 ? kAStages : 4), scale_bufs = 2;
   auto w_room = [&]() {
     return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
   };
   if (w_room() < 4) scale_bufs = 1;
-  if (w_room() < 3 && b_stages > 3) b_stages = 3;
-  if (w_room() < 3 && b_stages > 2) b_stages = 2;
+  while (w_room() < 3 && b_stages > 2) --b_stages;
   expects(w_room() >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
   p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
-  if (p.w_stages == kMaxWStages) {   // spare room: deepen the token ring too
+  if (p.w_stages == kMaxWStages || (CTAS == 2 && p.w_stages > 4)) {   // spare room: deepen the token ring
+    const int keep_w = CTAS == 2 ? 4 : kMaxWStages;
     while (b_stages < kAStages && b_stages < kMaxBStages &&
-           (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWStageBytes >=
-               kMaxWStages)
+           (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWStageBytes >= keep_w)
       ++b_stages;
+    p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
   }
   p.b_stages = b_stages;
   p.scale_bufs = scale_bufs;
@@ -914,20 +1041,37 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWStageBytes;
   static bool configured = false;
   if (!configured) {
-    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS>,
+    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     configured = true;
   }
-  moe_gemm_sm100_kernel<GATEUP, KS><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+  if (CTAS == 1) {
+    moe_gemm_sm100_kernel<GATEUP, KS, CTAS><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+  } else {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(sm_count() & ~1));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_gemm_sm100_kernel<GATEUP, KS, CTAS>, tw, tb, tb64, p));
+  }
 }
 
-// Stage length by the largest token tile of the launch (see the kernel's comment).
+// Stage length and CTA grouping by the largest token tile of the launch (see the kernel's comment).
 template <bool GATEUP>
 void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                  cudaStream_t stream) {
-  if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256>(tw, tb, tb64, p, stream);
-  else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128>(tw, tb, tb64, p, stream);
-  else launch_gemm_ks<GATEUP, 64>(tw, tb, tb64, p, stream);
+  if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
+  else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
+  else if (pair_mode()) launch_gemm_ks<GATEUP, 64, 2>(tw, tb, tb64, p, stream);
+  else launch_gemm_ks<GATEUP, 64, 1>(tw, tb, tb64, p, stream);
 }
 
 }  // namespace
@@ -1025,6 +1169,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   int max_tok = ((M + block_size - 1) / block_size) * block_size;
   max_tok = ((max_tok + 15) / 16) * 16;
   if (max_tok > kMaxTok) max_tok = kMaxTok;
+  if (max_tok > 128) max_tok = (max_tok + 31) & ~31;   // a CTA pair stages half of the rows each
   build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                              n_tiles, max_tok_tiles(EM));
   gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, sorted_ids, expert_ids, block_size, EM,
