@@ -59,7 +59,7 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kThreads = 512;
 constexpr int kTmemCols = 512;
 constexpr int kEpiStageBytes = 2 * 32 * 64 * 2;   // gate/up epilogue staging (two rounds)
-constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
+constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of SM clock
 
 struct TokTile {
   int expert;
@@ -127,11 +127,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // role's ran out of iterations).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
+  // try_wait suspends the thread for a hardware-chosen slice, so the limit is kept in clock
+  // cycles rather than in poll iterations.
+  long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u) {
+    if ((it & 63u) == 63u) {
       if (*abort_flag) return false;
-      if (it > kSpinLimit) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitClocks) {
         *abort_flag = code;
         return false;
       }
@@ -143,12 +148,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_lanes(uint32_t bar, uint32_t parity, bool active,
                                                 volatile int* abort_flag, int code) {
   bool done = !active;
+  long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (!done) done = mbar_try_wait(bar, parity);
     if (__all_sync(0xFFFFFFFFu, done)) return true;
-    if ((it & 1023u) == 1023u) {
+    if ((it & 63u) == 63u) {
       int stop = *abort_flag;
-      if (!stop && it > kSpinLimit) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (!stop && now - t0 > kWaitLimitClocks) {
         *abort_flag = code;
         stop = 1;
       }
@@ -334,6 +342,10 @@ __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
 // ---------------------------------------------------------------------------
 // shared-memory carve-up
 // ---------------------------------------------------------------------------
+// Accumulator columns: a lone CTA sizes them by the stage length (long stages serve small token
+// tiles), a pair always holds up to 256 tokens.
+constexpr int acc_cols(int ks, int ctas) { return ctas == 2 ? 256 : (ks == 64 ? 256 : (ks == 128 ? 128 : 64)); }
+
 struct Barriers {
   uint64_t w_full[kMaxWStages], w_empty[kMaxWStages];
   uint64_t a_full[kMaxAStages];    // dequant warps -> MMA issuer (4 arrivals, one per TMEM lane quarter)
@@ -372,18 +384,22 @@ __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
-  constexpr int kAccCols = KS == 64 ? 256 : (KS == 128 ? 128 : 64);   // accumulator columns
+  constexpr int kAccCols = acc_cols(KS, CTAS);                        // accumulator columns
   constexpr int kACols = KS / 2;                                      // columns of one A slot
-  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // 8, 6, 3
+  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // lone CTA: 8, 6, 3; pair: 8, 4
   constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
   constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
   static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
-  static_assert(CTAS == 1 || KS == 64, "the CTA-pair form is built for 64-K stages");
+  static_assert(CTAS == 1 || KS <= 128, "the CTA-pair form takes 64-K or 128-K stages");
   // CTAS == 2: two CTAs of a cluster work on one item - 256 weight rows (128 per CTA, each CTA
   // dequantises its own) against ONE token tile of up to 256 tokens, of which each CTA stages only
   // half. The leader (even) CTA issues cta_group::2 MMAs that read both halves; every CTA keeps
   // its 128 accumulator rows in its own tensor memory. This halves the token bytes a CTA pulls
   // from L2 per flop and doubles the depth of the token ring that fits in shared memory.
+  // A pair keeps ONE ring: token slot i lives and dies with A slot i, and the token bytes are
+  // expected on the same barrier the dequant warps arrive on, so the MMA issuer polls a single
+  // barrier per stage.
+  constexpr bool kMerged = CTAS == 2;
   const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
 
@@ -406,7 +422,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->w_empty[i]), 8);
     }
     for (int i = 0; i < kMaxAStages; ++i) {
-      mbar_init(smem_u32(&bars->a_full[i]), 4 * CTAS);
+      mbar_init(smem_u32(&bars->a_full[i]), kMerged ? 4 * CTAS + 1 : 4);
       mbar_init(smem_u32(&bars->stage_done[i]), 1);
     }
     for (int i = 0; i < kMaxBStages; ++i) mbar_init(smem_u32(&bars->b_full[i]), 1);
@@ -452,7 +468,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int n_stages = (p.K + KS - 1) / KS;           // pipeline stages per item (last may be short)
   const int pitch = p.K / 32;                         // scale bytes per weight row
   const int n_wrows = GATEUP ? 2 * p.n_feat : p.n_feat;
-  const int slice_bytes = (p.max_tok / CTAS) * 128;   // one 64-K slice of a token stage (this CTA's rows)
+  // one 64-K slice of a token stage (this CTA's rows; a pair's MMA N is the tile rounded up to 32)
+  const int slice_bytes = CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) * 128 : p.max_tok * 128;
 
   if (warp == 0) {
     // ------------------- TMA producer: packed weights + scales ---------------
@@ -517,7 +534,37 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // Token slot of stage s is free once the MMAs of stage s - b_stages are done;
     // that event is stage_done of the A slot that stage used (b_stages <= kAStages,
     // so the barrier cannot have moved on to a later phase yet).
-    if (lane == 0) {
+    if (kMerged) {
+      if (lane == 0) {
+        Ring a;
+        bool ok = true;
+        for (int item = unit; item < n_items && ok; item += n_units) {
+          const TokTile tt = p.tiles[item / n_fgroups];
+          // MMA N = rows rounded up to 32; this CTA stages half of them. Rows past the tile are
+          // someone else's (or zero fill past the tensor): their columns are never read back.
+          const int half_rows = ((tt.n_rows + 31) >> 5) << 4;
+          const int my_row0 = tt.row0 + (int)cta_rank * half_rows;
+          for (int st = 0; st < n_stages; ++st) {
+            if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 3)) {
+              ok = false;
+              break;
+            }
+            const uint32_t bar = smem_u32(&bars->a_full[a.slot]);
+            const uint32_t dst = smem_u32(b_smem + a.slot * p.b_stage_bytes);
+            const int n_slices = min(kPieces, (p.K - st * KS) / 64);
+            if (leader) mbar_expect_tx(bar, 2 * half_rows * 128 * n_slices);
+            for (int sl = 0; sl < n_slices; ++sl) {
+              const uint32_t d = dst + sl * slice_bytes;
+              const int k0 = st * KS + sl * 64;
+              int r = 0;
+              for (; r + 64 <= half_rows; r += 64) tma_load_2d_pair(d + r * 128, &tmap_b64, k0, my_row0 + r, bar);
+              for (; r < half_rows; r += 16) tma_load_2d_pair(d + r * 128, &tmap_b, k0, my_row0 + r, bar);
+            }
+            a.advance(kAStages);
+          }
+        }
+      }
+    } else if (lane == 0) {
       Ring b, lag;           // lag trails b by b_stages stages, on the A ring
       int issued = 0;        // stages issued so far (all items)
       bool ok = true;
@@ -535,24 +582,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
           const int k0 = st * KS;
           const int n_slices = min(kPieces, (p.K - k0) / 64);
-          if (CTAS == 2) {
-            // MMA N = rows rounded up to 32; this CTA stages half of them. Rows past the tile are
-            // someone else's (or zero fill past the tensor): their columns are never read back.
-            const int half_rows = ((tt.n_rows + 31) >> 5) << 4;
-            const int my_row0 = tt.row0 + (int)cta_rank * half_rows;
-            if (leader) mbar_expect_tx(bar, 2 * half_rows * 128);
+          mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
+          for (int sl = 0; sl < n_slices; ++sl) {
             int r = 0;
-            for (; r + 64 <= half_rows; r += 64) tma_load_2d_pair(dst + r * 128, &tmap_b64, k0, my_row0 + r, bar);
-            for (; r < half_rows; r += 16) tma_load_2d_pair(dst + r * 128, &tmap_b, k0, my_row0 + r, bar);
-          } else {
-            mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
-            for (int sl = 0; sl < n_slices; ++sl) {
-              int r = 0;
-              for (; r + 64 <= tt.n_rows; r += 64)
-                tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
-              for (; r < tt.n_rows; r += 16)
-                tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
-            }
+            for (; r + 64 <= tt.n_rows; r += 64)
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
+            for (; r < tt.n_rows; r += 16)
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
           }
           b.advance(p.b_stages);
         }
@@ -563,13 +599,66 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // The whole warp stays converged: lanes 0 and 1 poll the A-ready and the
     // tokens-ready barrier of the stage in the SAME instruction (one poll latency
     // instead of two), lane 0 issues the MMAs and one commit per stage.
-    Ring a, b;
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t tmem_u = __shfl_sync(0xFFFFFFFFu, tmem_base, 0);
-    for (int item = unit; item < n_items && ok && leader; item += n_units) {
+    if (kMerged) {
+      // One thread's dependent instructions are the clock of this loop, so everything a stage
+      // needs (barrier addresses, tensor-memory column, token descriptor) is carried along and
+      // bumped per stage instead of being recomputed from the slot index.
+      const uint32_t ready0 = smem_u32(&bars->a_full[0]), done0 = smem_u32(&bars->stage_done[0]);
+      const uint32_t acc_full_bar = smem_u32(&bars->acc_full);
+      const uint32_t a0 = tmem_u + kAccCols;
+      const uint64_t desc_first = make_b_desc(smem_u32(b_smem));
+      const uint32_t desc_step = (uint32_t)p.b_stage_bytes >> 4, slice16 = (uint32_t)slice_bytes >> 4;
+      uint32_t ready = ready0, done = done0, a_addr = a0, phase = 0;
+      uint64_t desc = desc_first;
+      int slot = 0;
+      for (int item = unit; item < n_items && ok && leader; item += n_units) {
+        const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
+        const uint32_t idesc = make_idesc((n_rows_u + 31) & ~31, 256);
+        if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
+        tc_fence_after();
+        for (int st = 0; st < n_stages; ++st) {
+          if (!mbar_wait(ready, phase, abort_flag, 5)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (elect_one()) {
+            const int n_slices = min(kPieces, (p.K - st * KS) / 64);
+#pragma unroll
+            for (int sl = 0; sl < kPieces; ++sl) {
+              if (sl < n_slices) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                  tc_mma_ts_pair(tmem_u, a_addr + sl * 32 + kk * 8, desc + sl * slice16 + kk * 2, idesc,
+                                 (sl | kk) != 0 ? 1u : (st != 0 ? 1u : 0u));
+              }
+            }
+            tc_commit_pair(done);   // completion is announced in both CTAs of the pair
+            if (st == n_stages - 1) tc_commit_pair(acc_full_bar);
+          }
+          ready += 8;
+          done += 8;
+          a_addr += kACols;
+          desc += desc_step;
+          if (++slot == kAStages) {
+            slot = 0;
+            phase ^= 1u;
+            ready = ready0;
+            done = done0;
+            a_addr = a0;
+            desc = desc_first;
+          }
+        }
+        acc_phase ^= 1u;
+      }
+    }
+    Ring a, b;
+    for (int item = unit; item < n_items && ok && !kMerged; item += n_units) {
       const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
-      const uint32_t idesc = CTAS == 2 ? make_idesc((n_rows_u + 31) & ~31, 256) : make_idesc(n_rows_u);
+      const uint32_t idesc = make_idesc(n_rows_u);
       if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
       tc_fence_after();
       for (int st = 0; st < n_stages; ++st) {
@@ -590,21 +679,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (sl < n_slices) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                if (CTAS == 2)
-                  tc_mma_ts_pair(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
-                                 (st | sl | kk) != 0 ? 1u : 0u);
-                else
-                  tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
-                            (st | sl | kk) != 0 ? 1u : 0u);
+                tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                          (st | sl | kk) != 0 ? 1u : 0u);
             }
           }
-          if (CTAS == 2) {   // completion is announced in both CTAs of the pair
-            tc_commit_pair(smem_u32(&bars->stage_done[a.slot]));
-            if (st == n_stages - 1) tc_commit_pair(smem_u32(&bars->acc_full));
-          } else {
-            tc_commit(smem_u32(&bars->stage_done[a.slot]));
-            if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
-          }
+          tc_commit(smem_u32(&bars->stage_done[a.slot]));
+          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
         }
         __syncwarp();
         a.advance(kAStages);
@@ -1006,6 +1086,15 @@ bool pair_mode() {
   return on;
 }
 
+// Whether the CTA-pair form fits shared memory: one token slot per A slot, one scale buffer,
+// at least two packed-weight stages.
+bool pair_fits(const GemmParams& p, bool gateup) {
+  const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (gateup ? kEpiStageBytes : 0) + 128;
+  const int tokens = 8 * (((p.max_tok + 31) >> 5) << 4) * 128;   // 8 x 64-K or 4 x 128-K slots
+  return 227 * 1024 - fixed - scale_tile - tokens >= 2 * kWStageBytes;
+}
+
 template <bool GATEUP, int KS, int CTAS>
 void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                     cudaStream_t stream) {
@@ -1013,23 +1102,24 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   // barriers, epilogue staging; what is left becomes the packed-weight ring (3..8 stages of
   // 16 KB): the deeper it is, the more weight bytes are in flight, which is what a decode-size
   // batch is bound by.
-  constexpr int kAccCols = KS == 64 ? 256 : (KS == 128 ? 128 : 64);
+  constexpr int kAccCols = acc_cols(KS, CTAS);
   constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : 0) + 128;
-  p.b_stage_bytes = (p.max_tok / CTAS) * 128 * (KS / 64);
-  // token ring: 4 slots for a lone CTA; a pair stages half the rows per CTA and takes 6
-  int b_stages = CTAS == 2 ? 6 : (kAStages < 4 ? kAStages : 4), scale_bufs = 2;
+  // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
+  p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
+  // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot
+  int b_stages = CTAS == 2 ? kAStages : (kAStages < 4 ? kAStages : 4), scale_bufs = 2;
   auto w_room = [&]() {
     return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
   };
   if (w_room() < 4) scale_bufs = 1;
-  while (w_room() < 3 && b_stages > 2) --b_stages;
+  while (CTAS == 1 && w_room() < 3 && b_stages > 2) --b_stages;
   expects(w_room() >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
   p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
-  if (p.w_stages == kMaxWStages || (CTAS == 2 && p.w_stages > 4)) {   // spare room: deepen the token ring
-    const int keep_w = CTAS == 2 ? 4 : kMaxWStages;
+  if (CTAS == 1 && p.w_stages == kMaxWStages) {   // spare room: deepen the token ring
+    const int keep_w = kMaxWStages;
     while (b_stages < kAStages && b_stages < kMaxBStages &&
            (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWStageBytes >= keep_w)
       ++b_stages;
@@ -1070,7 +1160,11 @@ void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap
                  cudaStream_t stream) {
   if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
-  else if (pair_mode()) launch_gemm_ks<GATEUP, 64, 2>(tw, tb, tb64, p, stream);
+  else if (pair_mode() && pair_fits(p, GATEUP)) {
+    static const bool ks64 = [] { const char* e = std::getenv("VK_MOE_PAIR_KS"); return e && std::atoi(e) == 64; }();
+    if (ks64) launch_gemm_ks<GATEUP, 64, 2>(tw, tb, tb64, p, stream);
+    else launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
+  }
   else launch_gemm_ks<GATEUP, 64, 1>(tw, tb, tb64, p, stream);
 }
 
