@@ -49,7 +49,12 @@ namespace {
 // ---------------------------------------------------------------------------
 // geometry
 // ---------------------------------------------------------------------------
-constexpr int kMaxTok = 256;        // tokens (MMA N) per work item
+constexpr int kMaxTok = 256;        // tokens (MMA N) per work item of a lone CTA
+// A CTA pair takes up to 320 tokens per item: a 256-column accumulator plus a 64-column one
+// fed by a second MMA per K block. An expert whose token count is a little over 256 (the common
+// case when tokens spread evenly) then costs one pass over its weights instead of two.
+constexpr int kPairMainTok = 256;
+constexpr int kPairMaxTok = 320;
 constexpr int kRows = 128;          // weight rows (MMA M) per work item
 constexpr int kWStageK = 256;       // K elements per packed-weight stage (128 B per row)
 constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per launch (3..8)
@@ -64,7 +69,7 @@ constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of S
 struct TokTile {
   int expert;
   int row0;
-  int n_rows;  // multiple of 16, <= kMaxTok
+  int n_rows;  // multiple of 16, <= kMaxTok (kPairMaxTok for CTA pairs)
   int pad;
 };
 
@@ -110,16 +115,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// The suspend-time hint keeps a waiting warp parked in hardware instead of spinning through
+// the poll loop: a dozen waiting warps per CTA otherwise take issue slots and integer-pipe
+// cycles from the dequant warps.
+constexpr uint32_t kSuspendHintNs = 20000u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -343,8 +352,8 @@ __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
 // shared-memory carve-up
 // ---------------------------------------------------------------------------
 // Accumulator columns: a lone CTA sizes them by the stage length (long stages serve small token
-// tiles), a pair always holds up to 256 tokens.
-constexpr int acc_cols(int ks, int ctas) { return ctas == 2 ? 256 : (ks == 64 ? 256 : (ks == 128 ? 128 : 64)); }
+// tiles), a pair always holds up to kPairMaxTok tokens.
+constexpr int acc_cols(int ks, int ctas) { return ctas == 2 ? kPairMaxTok : (ks == 64 ? 256 : (ks == 128 ? 128 : 64)); }
 
 struct Barriers {
   uint64_t w_full[kMaxWStages], w_empty[kMaxWStages];
@@ -355,8 +364,8 @@ struct Barriers {
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
   int abort_flag;
-  int tile_tok[kMaxTok];
-  float tile_w[kMaxTok];
+  int tile_tok[kPairMaxTok];
+  float tile_w[kPairMaxTok];
 };
 
 // Ring position: slot index and phase parity, advanced without division.
@@ -386,7 +395,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
   constexpr int kAccCols = acc_cols(KS, CTAS);                        // accumulator columns
   constexpr int kACols = KS / 2;                                      // columns of one A slot
-  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // lone CTA: 8, 6, 3; pair: 8, 4
+  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // lone CTA: 8, 6, 3; pair: 6, 3
   constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
   constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
   static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
@@ -540,10 +549,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         bool ok = true;
         for (int item = unit; item < n_items && ok; item += n_units) {
           const TokTile tt = p.tiles[item / n_fgroups];
-          // MMA N = rows rounded up to 32; this CTA stages half of them. Rows past the tile are
-          // someone else's (or zero fill past the tensor): their columns are never read back.
-          const int half_rows = ((tt.n_rows + 31) >> 5) << 4;
-          const int my_row0 = tt.row0 + (int)cta_rank * half_rows;
+          // The tile, rounded up to 32 rows, is split into a main part (<= 256 rows, first MMA)
+          // and an extension (<= 64 rows, second MMA); this CTA stages half of each. Rows past
+          // the tile are someone else's (or zero fill past the tensor): their columns are never
+          // read back.
+          const int n32 = (tt.n_rows + 31) & ~31;
+          const int h0 = min(n32, kPairMainTok) >> 1, h1 = (n32 >> 1) - h0;
+          const int row_main = tt.row0 + (int)cta_rank * h0;
+          const int row_ext = tt.row0 + 2 * h0 + (int)cta_rank * h1;
           for (int st = 0; st < n_stages; ++st) {
             if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 3)) {
               ok = false;
@@ -552,13 +565,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint32_t bar = smem_u32(&bars->a_full[a.slot]);
             const uint32_t dst = smem_u32(b_smem + a.slot * p.b_stage_bytes);
             const int n_slices = min(kPieces, (p.K - st * KS) / 64);
-            if (leader) mbar_expect_tx(bar, 2 * half_rows * 128 * n_slices);
+            if (leader) mbar_expect_tx(bar, 2 * (h0 + h1) * 128 * n_slices);
             for (int sl = 0; sl < n_slices; ++sl) {
               const uint32_t d = dst + sl * slice_bytes;
               const int k0 = st * KS + sl * 64;
               int r = 0;
-              for (; r + 64 <= half_rows; r += 64) tma_load_2d_pair(d + r * 128, &tmap_b64, k0, my_row0 + r, bar);
-              for (; r < half_rows; r += 16) tma_load_2d_pair(d + r * 128, &tmap_b, k0, my_row0 + r, bar);
+              for (; r + 64 <= h0; r += 64) tma_load_2d_pair(d + r * 128, &tmap_b64, k0, row_main + r, bar);
+              for (; r < h0; r += 16) tma_load_2d_pair(d + r * 128, &tmap_b, k0, row_main + r, bar);
+              for (r = 0; r < h1; r += 16) tma_load_2d_pair(d + (h0 + r) * 128, &tmap_b, k0, row_ext + r, bar);
             }
             a.advance(kAStages);
           }
@@ -616,7 +630,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       int slot = 0;
       for (int item = unit; item < n_items && ok && leader; item += n_units) {
         const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
-        const uint32_t idesc = make_idesc((n_rows_u + 31) & ~31, 256);
+        const int n32 = (n_rows_u + 31) & ~31;
+        const int n_main = min(n32, kPairMainTok), n_ext = n32 - n_main;
+        const uint32_t idesc = make_idesc(n_main, 256), idesc_ext = make_idesc(n_ext, 256);
+        const uint32_t ext16 = (uint32_t)(n_main >> 1) * 8u;   // descriptor offset of the extension rows
         if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
         tc_fence_after();
         for (int st = 0; st < n_stages; ++st) {
@@ -631,9 +648,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             for (int sl = 0; sl < kPieces; ++sl) {
               if (sl < n_slices) {
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                  tc_mma_ts_pair(tmem_u, a_addr + sl * 32 + kk * 8, desc + sl * slice16 + kk * 2, idesc,
-                                 (sl | kk) != 0 ? 1u : (st != 0 ? 1u : 0u));
+                for (int kk = 0; kk < 4; ++kk) {
+                  const uint32_t acc = (sl | kk) != 0 ? 1u : (st != 0 ? 1u : 0u);
+                  tc_mma_ts_pair(tmem_u, a_addr + sl * 32 + kk * 8, desc + sl * slice16 + kk * 2, idesc, acc);
+                  if (n_ext != 0)
+                    tc_mma_ts_pair(tmem_u + kPairMainTok, a_addr + sl * 32 + kk * 8,
+                                   desc + ext16 + sl * slice16 + kk * 2, idesc_ext, acc);
+                }
               }
             }
             tc_commit_pair(done);   // completion is announced in both CTAs of the pair
@@ -1091,7 +1112,7 @@ bool pair_mode() {
 bool pair_fits(const GemmParams& p, bool gateup) {
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (gateup ? kEpiStageBytes : 0) + 128;
-  const int tokens = 8 * (((p.max_tok + 31) >> 5) << 4) * 128;   // 8 x 64-K or 4 x 128-K slots
+  const int tokens = 6 * (((p.max_tok + 31) >> 5) << 4) * 128;   // 6 x 64-K or 3 x 128-K slots
   return 227 * 1024 - fixed - scale_tile - tokens >= 2 * kWStageBytes;
 }
 
@@ -1157,10 +1178,10 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
 // Stage length and CTA grouping by the largest token tile of the launch (see the kernel's comment).
 template <bool GATEUP>
 void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
-                 cudaStream_t stream) {
+                 bool use_pair, cudaStream_t stream) {
   if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
-  else if (pair_mode() && pair_fits(p, GATEUP)) {
+  else if (use_pair) {
     static const bool ks64 = [] { const char* e = std::getenv("VK_MOE_PAIR_KS"); return e && std::atoi(e) == 64; }();
     if (ks64) launch_gemm_ks<GATEUP, 64, 2>(tw, tb, tb64, p, stream);
     else launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
@@ -1262,8 +1283,18 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // A token meets an expert at most once, so no expert holds more than M rows (+ padding).
   int max_tok = ((M + block_size - 1) / block_size) * block_size;
   max_tok = ((max_tok + 15) / 16) * 16;
-  if (max_tok > kMaxTok) max_tok = kMaxTok;
-  if (max_tok > 128) max_tok = (max_tok + 31) & ~31;   // a CTA pair stages half of the rows each
+  // Tiles over 128 tokens go to CTA pairs when both GEMMs fit shared memory in that form.
+  bool use_pair = false;
+  if (max_tok > 128 && pair_mode()) {
+    GemmParams probe{};
+    probe.max_tok = max_tok > kPairMaxTok ? kPairMaxTok : ((max_tok + 31) & ~31);
+    probe.K = hidden;
+    use_pair = pair_fits(probe, true);
+    probe.K = ispp;
+    use_pair = use_pair && pair_fits(probe, false);
+    if (use_pair) max_tok = probe.max_tok;   // a CTA pair stages half of the rows each
+  }
+  if (!use_pair && max_tok > kMaxTok) max_tok = kMaxTok;
   build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                              n_tiles, max_tok_tiles(EM));
   gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, sorted_ids, expert_ids, block_size, EM,
@@ -1285,7 +1316,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
     const CUtensorMap tb64 = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
                                       (uint64_t)hidden * 2, 64, 64);
     timer_mark(0, stream);
-    launch_gemm<true>(tw, tb, tb64, p, stream);
+    launch_gemm<true>(tw, tb, tb64, p, use_pair, stream);
     timer_mark(1, stream);
   }
   {  // down + combine
@@ -1298,7 +1329,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                                     (uint64_t)ispp * 2, 64, 16);
     const CUtensorMap tb64 = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
                                       (uint64_t)ispp * 2, 64, 64);
-    launch_gemm<false>(tw, tb, tb64, p, stream);
+    launch_gemm<false>(tw, tb, tb64, p, use_pair, stream);
     timer_mark(2, stream);
   }
   VK_CUDA_CHECK(cudaGetLastError());
