@@ -330,13 +330,53 @@ def run_multi_gpu(args, cfg, T):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
+    from vkernels_b200 import torch_ops as ops
+    ops.kernel_status()
+
+    # this rank's two GEMM kernels (every rank times its own; rank 0 reports its pair)
+    layer.count_local_slots = True
+    g_ms, d_ms, _ = kernel_times(step, max(3, min(args.steps, 10)))
     stats = layer.last_stats()
+    layer.count_local_slots = False
+    peaks = measured_peaks()
+    tensor_peak = peaks["bf16_tflops_sustained"]
+    flops_gateup = 4 * stats["local_slots"] * cfg.I * cfg.H
+    achieved = flops_gateup / (g_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "moe_gemm_sm100_kernel<gate/up> (rank 0)", "achieved": achieved,
+                "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
+                "traffic": None, "algorithmic_flops_per_launch": flops_gateup, "ms_per_launch": g_ms,
+                "down_kernel": {"achieved": flops_gateup / 2 / (d_ms * 1e-3) / 1e12, "ms_per_launch": d_ms,
+                                "frac": flops_gateup / 2 / (d_ms * 1e-3) / 1e12 / tensor_peak}}
+
+    # end to end: every rank copies its token slice from pinned host memory, runs the sharded
+    # layer and reads its output rows back; wall clock between barriers, max over ranks
+    xh = A.cpu().pin_memory()
+    yh = torch.empty((T_local, cfg.H), dtype=torch.bfloat16).pin_memory()
+    xd = torch.empty_like(A)
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        yh.copy_(layer(xd), non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        e2e_step()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    te = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=dev)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item())
+    e2e = {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.H * 2,
+           "d2h_bytes_per_step": T * cfg.H * 2, "ms_per_step": e2e_ms}
     if rank == 0:
         line = {"metric": METRIC, "value": T / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32", "data": "synthetic",
-                "config": workload_config(cfg, T, world), "roofline": None, "cpu_baseline": None,
-                "e2e": None, "gpu_launches": stats["launches_per_step"] * args.steps, "clocks": clk.summary(),
+                "config": workload_config(cfg, T, world), "roofline": roofline, "cpu_baseline": None,
+                "e2e": e2e, "gpu_launches": stats["launches_per_step"] * args.steps, "clocks": clk.summary(),
                 "ep": stats}
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -1,0 +1,89 @@
+"""Expert parallelism on real GPUs: two NCCL ranks, each holding a contiguous slice of the experts,
+exchange token rows with all_to_all_single and must reproduce the single-rank layer (and the CPU
+oracle) on every rank's own tokens. The counterpart of the reference's two-rank EP check
+(tests/c/test_dist_moe.cpp), with its in-process ranks replaced by one process per GPU.
+
+Needs two visible GPUs; skipped otherwise."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    try:
+        import oracle
+        from helpers import bf16_to_u16
+        from vkernels_b200 import synthetic as syn
+        from vkernels_b200.dist import ExpertParallelMoE
+        from vkernels_b200.experts import layer_from_config
+
+        cfg = syn.scaled(syn.CONFIGS["c0"], E=6, top_k=3)   # 6 experts over 2 ranks, uneven use
+        T_local = 48
+        T = T_local * world
+        ep = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T_local)
+        A = syn.make_activations(cfg, T, backend="torch", device=dev, seed=cfg.seed)
+        lo, hi = rank * T_local, (rank + 1) * T_local
+
+        # routed by this rank's router on its own tokens
+        y = ep(A[lo:hi].contiguous())
+        torch.cuda.synchronize()
+        stats = ep.last_stats()
+
+        # single-rank layer with all experts on this GPU, same seeded weights and router
+        wt = syn.make_expert_weights(cfg, backend="torch", device=dev)
+        full = layer_from_config(cfg, wt, syn.make_router(cfg, device=dev), max_tokens=T)
+        ids, w = full.route(A)
+        y_full = full.experts(A, ids, w)
+        torch.cuda.synchronize()
+        got = y.float().cpu().numpy()
+        want = y_full[lo:hi].float().cpu().numpy()
+        scale = max(float(np.abs(want).max()), 1.0)
+        # fp32 partial sums are rounded to bf16 once on both paths; the ranks add their partial
+        # rows in rank order, the single-rank layer in expert order: one bf16 ulp of slack
+        err_single = float(np.max(np.abs(got - want)))
+        ok = err_single <= 2 ** -7 * scale
+
+        # the CPU oracle on the same routing
+        wts = {k: v.cpu().numpy() for k, v in wt.items()}
+        ref = oracle.moe_layer(bf16_to_u16(A.cpu()), wts["w13"], wts["w13_scale"], wts["w2"], wts["w2_scale"],
+                               ids[:, : cfg.top_k].cpu().numpy(), w[:, : cfg.top_k].cpu().numpy(), num_experts=cfg.E)
+        err_oracle = float(np.max(np.abs(got - ref[lo:hi])))
+        ok = ok and err_oracle <= 2 ** -6 * scale
+        ok = ok and T_local <= stats["rows_sent"] <= T_local * world
+        open(os.path.join(tmp, f"rank{rank}.txt"), "w").write(
+            f"{int(ok)} err_single={err_single} err_oracle={err_oracle} scale={scale} {stats}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_ranks_match_single_rank(tmp_path, oracle_mod):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        txt = (tmp_path / f"rank{r}.txt").read_text()
+        assert txt.startswith("1"), f"rank {r}: {txt}"

@@ -94,6 +94,7 @@ class ExpertParallelMoE:
         self.begins_host = expert_begins(num_experts, self.world)
         self.begins = torch.tensor(self.begins_host, dtype=torch.int32, device=self.device)
         self._stats = {}
+        self.count_local_slots = False   # last_stats()["local_slots"]: one extra host read per step
 
     @classmethod
     def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
@@ -160,6 +161,7 @@ class ExpertParallelMoE:
             part = self.backend.experts(recv_x[:R_recv], recv_ids[:R_recv], recv_w[:R_recv])
         else:
             part = torch.zeros((0, H), dtype=torch.float32, device=dev)
+        local_slots = int((recv_ids[:R_recv] >= 0).sum()) if self.count_local_slots else None
         # 6. return
         back = torch.empty((max(R_send, 1), H), dtype=torch.float32, device=dev)
         dist.all_to_all_single(back[:R_send], part, send_n, recv_n, group=self.group)
@@ -168,7 +170,8 @@ class ExpertParallelMoE:
         self.backend.combine(back, row_of, T, H, world, out)
         self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T,
                        "launches_per_step": 2 + 2 + 1 + (1 if R_recv * slots <= 1024 else 3) + 4,
-                       "dispatch_bytes": R_send * (H * 2 + slots * 8), "combine_bytes": R_recv * H * 4}
+                       "dispatch_bytes": R_send * (H * 2 + slots * 8), "combine_bytes": R_recv * H * 4,
+                       "local_slots": local_slots}
         return out
 
     __call__ = forward

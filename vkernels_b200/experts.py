@@ -97,6 +97,9 @@ class FusedMoEMxfp4:
         self.swiglu_limit, self.activation, self.beta, self.linear_beta = (swiglu_limit, activation,
                                                                           beta, linear_beta)
         self.router_weight, self.router_bias = router_weight, router_bias
+        # the router scores every routed expert of the model; under expert parallelism this
+        # layer holds only a slice of them
+        self.n_router = self.n_routed if router_weight is None else router_weight.shape[0]
         self.block_size = block_size
         self.max_tokens = max_tokens or max_num_tokens_hint()
         self.scratch = CaptureSafeScratch()
@@ -122,7 +125,7 @@ class FusedMoEMxfp4:
         em = self._em_bound(T)
         g = lambda key, n, dt, cap: s.get(key, n, dtype=dt, device=d, capacity=cap, name=str(key))
         return {
-            "logits": g("logits", T * self.n_routed, torch.float32, cap_t * self.n_routed),
+            "logits": g("logits", T * self.n_router, torch.float32, cap_t * self.n_router),
             "ids": g("ids", T * self.slots, torch.int32, cap_t * self.slots),
             "w": g("w", T * self.slots, torch.float32, cap_t * self.slots),
             "sids": g("sids", em, torch.int32, cap_em),
@@ -143,7 +146,7 @@ class FusedMoEMxfp4:
             if self.router_weight is None:
                 raise TypeError("this layer has no router weight; pass logits or topk ids")
             logits = ops.router_logits(x, self.router_weight,
-                                       out=bufs["logits"].view(T, self.n_routed))
+                                       out=bufs["logits"].view(T, self.n_router))
         ids = bufs["ids"].view(T, self.slots)
         w = bufs["w"].view(T, self.slots)
         ops.route_topk(logits, self.top_k, bias=self.router_bias,

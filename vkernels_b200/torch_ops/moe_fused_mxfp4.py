@@ -87,6 +87,7 @@ def router_logits(x: torch.Tensor, wr: torch.Tensor, out: torch.Tensor | None = 
     E = wr.shape[0]
     if out is None:
         out = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    require(out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous(), "out must be fp32 [T, E]")
     with torch.cuda.device(x.device):
         nr.check(nr.load_library().vk_cuda_moe_router_logits(_ptr(x), _ptr(wr), _ptr(out), T, H, E,
                                                             _stream(x)), "router_logits")
