@@ -124,17 +124,27 @@ def _check_route(cfg, T, logits=None, seed=None):
     if logits is None:
         lg = ops.router_logits(A, r["wr"])
         ref_logits = oracle.router_logits(bf16_to_u16(A), to_np(r["wr"]))
-        assert np.allclose(to_np(lg), ref_logits, rtol=2e-5, atol=2e-6)
+        # Both sides round an fp32 sum of H exact products, in different orders (the oracle adds
+        # sequentially, the device adds tensor-core partial sums of 64 products). The yardstick is
+        # the oracle's own rounding noise against the float64 dot: the device must be at least
+        # as close to the exact value, and the two may differ by no more than twice that noise.
+        exact = A.float().cpu().numpy().astype(np.float64) @ to_np(r["wr"]).astype(np.float64).T
+        noise = float(np.abs(ref_logits - exact).max())
+        assert float(np.abs(to_np(lg) - exact).max()) <= noise + 2e-6
+        assert float(np.abs(to_np(lg) - ref_logits).max()) <= 2 * noise + 2e-6
     else:
         lg = logits
         ref_logits = to_np(logits)
+        noise = 0.0
     ids, w = ops.route_topk(lg, cfg.top_k, bias=r["bias"], sigmoid=cfg.routing == "sigmoid_group",
                             n_group=cfg.n_group, topk_group=cfg.topk_group, renorm=cfg.renorm,
                             scaling=cfg.scaling, n_shared=cfg.shared_experts)
     rid, rw, margin = oracle_route(cfg, A, r, logits=ref_logits)
     # tokens whose every pick is decided by more than fp32 reassociation noise (the device sums
     # the logits and the softmax denominator in another order; observed differences are ~1e-6)
-    ok = margin > 2e-5
+    # scores move by at most a quarter of a logit change (softmax and sigmoid slopes), the two
+    # logit sets differ by at most 2 * noise, so a margin above `noise` cannot flip a pick
+    ok = margin > max(2e-5, noise)
     assert ok.mean() > 0.9, f"only {ok.mean():.3f} of the tokens are well separated"
     assert np.array_equal(to_np(ids)[ok], rid[ok]), "routing indices differ"
     assert np.allclose(to_np(w)[ok], rw[ok], rtol=1e-4, atol=1e-6)

@@ -71,6 +71,156 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
   }
 }
 
+// ----------------------------- tensor-core router GEMM ----------------------
+// Large batches. The fp32 router weight is split on the fly into three bf16 terms
+// (w = hi + mid + lo exactly: 3 x 8 mantissa bits), the activations are bf16 already, so
+// every product is exact in fp32. Partial sums over 64 K-elements are formed by
+// mma.sync.m16n8k16 (smallest terms first) and added to the running fp32 totals in
+// registers, which keeps the result within fp32 reassociation noise of a sequential fp32 dot.
+// CTA: 64 tokens x 128 experts, 8 warps as 4 (tokens) x 2 (experts); warp tile 16 x 64.
+constexpr int MT = 64, ME = 128, MK = 64, MPAD = 8;   // +8 bf16 per row: conflict-free ldmatrix
+constexpr int MROW = MK + MPAD;
+
+struct RouterSmem {
+  uint16_t x[2][MT][MROW];
+  uint16_t w[2][3][ME][MROW];
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// w -> (hi, mid, lo) bf16 bit patterns with hi + mid + lo == w (round to nearest at each step)
+__device__ __forceinline__ void split3(float w, uint16_t& hi, uint16_t& mid, uint16_t& lo) {
+  hi = f32_to_bf16_bits(w);
+  const float r1 = w - bf16_bits_to_f32(hi);
+  mid = f32_to_bf16_bits(r1);
+  const float r2 = r1 - bf16_bits_to_f32(mid);
+  lo = f32_to_bf16_bits(r2);
+}
+
+__global__ void __launch_bounds__(256)
+router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict__ wr,
+                         float* __restrict__ logits, int T, int H, int E) {
+  extern __shared__ __align__(16) uint8_t router_smem_raw[];
+  RouterSmem& sm = *reinterpret_cast<RouterSmem*>(router_smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t0 = blockIdx.x * MT, e0 = blockIdx.y * ME;
+  const int wt = warp & 3, we = warp >> 2;   // warp tile: tokens wt*16.., experts we*64..
+
+  // global -> register staging of one K chunk: x 64 x 64 bf16 (2 x 16 B per thread),
+  // w 128 x 64 fp32 (8 x 16 B per thread)
+  uint4 xr[2];
+  float4 wv[8];
+  auto load_chunk = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * 256;           // 0..511: row = idx / 8, 8 bf16 at (idx % 8) * 8
+      const int r = idx >> 3, c = (idx & 7) * 8;
+      const int t = t0 + r, k = k0 + c;
+      xr[i] = (t < T && k < H) ? *reinterpret_cast<const uint4*>(x + (size_t)t * H + k)
+                               : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 256;           // 0..2047: row = idx / 16, 4 fp32 at (idx % 16) * 4
+      const int r = idx >> 4, c = (idx & 15) * 4;
+      const int e = e0 + r, k = k0 + c;
+      wv[i] = (e < E && k < H) ? *reinterpret_cast<const float4*>(wr + (size_t)e * H + k)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto store_chunk = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * 256;
+      *reinterpret_cast<uint4*>(&sm.x[buf][idx >> 3][(idx & 7) * 8]) = xr[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx >> 4, c = (idx & 15) * 4;
+      const float f[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+      uint16_t h[4], m[4], l[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) split3(f[j], h[j], m[j], l[j]);
+      *reinterpret_cast<uint2*>(&sm.w[buf][0][r][c]) =
+          make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+      *reinterpret_cast<uint2*>(&sm.w[buf][1][r][c]) =
+          make_uint2((uint32_t)m[0] | ((uint32_t)m[1] << 16), (uint32_t)m[2] | ((uint32_t)m[3] << 16));
+      *reinterpret_cast<uint2*>(&sm.w[buf][2][r][c]) =
+          make_uint2((uint32_t)l[0] | ((uint32_t)l[1] << 16), (uint32_t)l[2] | ((uint32_t)l[3] << 16));
+    }
+  };
+
+  float total[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) total[n][j] = 0.0f;
+
+  const int n_chunks = (H + MK - 1) / MK;
+  load_chunk(0);
+  store_chunk(0);
+  __syncthreads();
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int buf = ch & 1;
+    if (ch + 1 < n_chunks) load_chunk((ch + 1) * MK);
+    float part[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) part[n][j] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < MK / 16; ++ks) {
+      uint32_t a[4];
+      // lanes 0-15: rows 0-15 at k, lanes 16-31: rows 0-15 at k + 8
+      ldmatrix_x4(a, &sm.x[buf][wt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int term = 2; term >= 0; --term) {   // lo, mid, hi
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {         // two 8-expert tiles per ldmatrix.x4
+          uint32_t b[4];
+          // matrices: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+          const int row = we * 64 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int col = ks * 16 + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4(b, &sm.w[buf][term][row][col]);
+          mma_bf16_16816(part[np * 2], a, b[0], b[1]);
+          mma_bf16_16816(part[np * 2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) total[n][j] += part[n][j];
+    if (ch + 1 < n_chunks) store_chunk(buf ^ 1);
+    __syncthreads();
+  }
+  // c fragment: rows lane / 4 and + 8, columns (lane % 4) * 2 and + 1
+  const int r0 = t0 + wt * 16 + (lane >> 2);
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    const int e = e0 + we * 64 + n * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = r0 + half * 8;
+      if (t >= T) continue;
+      if (e < E) logits[(size_t)t * E + e] = total[n][half * 2];
+      if (e + 1 < E) logits[(size_t)t * E + e + 1] = total[n][half * 2 + 1];
+    }
+  }
+}
+
 // Small batches: one warp per (token, expert) dot product, 128-bit loads, so a decode
 // step fills the machine instead of running on a couple of CTAs.
 __global__ void __launch_bounds__(256)
@@ -263,6 +413,17 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
   if (T <= 512 && H % 4 == 0) {
     const long long pairs = (long long)T * E;
     router_logits_warp_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, wr, logits, T, H, E);
+  } else if (H % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+             (reinterpret_cast<uintptr_t>(wr) & 15u) == 0) {
+    static bool configured = false;
+    if (!configured) {
+      VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(RouterSmem)));
+      configured = true;
+    }
+    dim3 grid((T + MT - 1) / MT, (E + ME - 1) / ME);
+    router_logits_mma_kernel<<<grid, 256, sizeof(RouterSmem), static_cast<cudaStream_t>(stream)>>>(
         x, wr, logits, T, H, E);
   } else {
     dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
