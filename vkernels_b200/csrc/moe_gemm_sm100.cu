@@ -64,6 +64,7 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 constexpr int kThreads = 512;
 constexpr int kTmemCols = 512;
 constexpr int kEpiStageBytes = 2 * 32 * 64 * 2;   // gate/up epilogue staging (two rounds)
+constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
 constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of SM clock
 
 struct TokTile {
@@ -280,6 +281,11 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
+}
+// out[0..3] += (a, b, c, d): one 16-byte reduction (address 16-byte aligned).
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -894,25 +900,60 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
       } else {
         const int rows_valid = min(128, p.n_feat - f * 128);
-        const int hcol = f * 128 + etid;
-        const bool row_ok = etid < rows_valid;
-        const float b = (p.bias && row_ok) ? p.bias[(size_t)tt.expert * p.n_feat + hcol] : 0.0f;
-        for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
-          uint32_t v[32];
-          tc_ld32(t_lane + c0, v);
-          tc_wait_ld();
-          if (c0 + 32 >= tt.n_rows) release_acc();
-          // lane l keeps token and routing weight of column c0 + l; the loop broadcasts them by
-          // shuffle, so no reduction below waits on a shared-memory load
-          const int my_t = c0 + lane;
-          const int my_tok = my_t < tt.n_rows ? bars->tile_tok[my_t] : -1;
-          const float my_w = my_t < tt.n_rows ? bars->tile_w[my_t] : 0.0f;
+        if ((p.n_feat & 3) == 0) {
+          // 16-byte reductions: the warp turns its 32 rows x 32 tokens block around through
+          // shared memory, so a lane holds four consecutive output features of one token and
+          // adds them with one red.v4 (a quarter of the reduction instructions, which are what
+          // this epilogue is bound by). Lane l: features 4 * (l % 8).., tokens l / 8 + 4 * i.
+          float* stage = reinterpret_cast<float*>(epi_stage) + q * (32 * 32);
+          const int hq = (lane & 7) * 4;                 // feature quad inside the warp's 32 rows
+          const int h0 = f * 128 + q * 32 + hq;
+          const bool quad_ok = q * 32 + hq < rows_valid;
+          float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.bias && quad_ok) b4 = *reinterpret_cast<const float4*>(p.bias + (size_t)tt.expert * p.n_feat + h0);
+          for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+            uint32_t v[32];
+            tc_ld32(t_lane + c0, v);
+            tc_wait_ld();
+            if (c0 + 32 >= tt.n_rows) release_acc();
+            __syncwarp();   // the previous block has been read
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int token = __shfl_sync(0xFFFFFFFFu, my_tok, j);
-            const float wgt = __shfl_sync(0xFFFFFFFFu, my_w, j);
-            if (token >= 0 && row_ok)
-              atomicAdd(p.out + (size_t)token * p.n_feat + hcol, (__uint_as_float(v[j]) + b) * wgt);
+            for (int j = 0; j < 32; ++j) stage[j * 32 + lane] = __uint_as_float(v[j]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int tl = (lane >> 3) + 4 * i;
+              const int t = c0 + tl;
+              const int token = t < tt.n_rows ? bars->tile_tok[t] : -1;
+              if (token >= 0 && quad_ok) {
+                const float wgt = bars->tile_w[t];
+                const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                red_add_v4(p.out + (size_t)token * p.n_feat + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
+                           (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
+              }
+            }
+          }
+        } else {
+          const int hcol = f * 128 + etid;
+          const bool row_ok = etid < rows_valid;
+          const float b = (p.bias && row_ok) ? p.bias[(size_t)tt.expert * p.n_feat + hcol] : 0.0f;
+          for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+            uint32_t v[32];
+            tc_ld32(t_lane + c0, v);
+            tc_wait_ld();
+            if (c0 + 32 >= tt.n_rows) release_acc();
+            // lane l keeps token and routing weight of column c0 + l; the loop broadcasts them by
+            // shuffle, so no reduction below waits on a shared-memory load
+            const int my_t = c0 + lane;
+            const int my_tok = my_t < tt.n_rows ? bars->tile_tok[my_t] : -1;
+            const float my_w = my_t < tt.n_rows ? bars->tile_w[my_t] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int token = __shfl_sync(0xFFFFFFFFu, my_tok, j);
+              const float wgt = __shfl_sync(0xFFFFFFFFu, my_w, j);
+              if (token >= 0 && row_ok)
+                atomicAdd(p.out + (size_t)token * p.n_feat + hcol, (__uint_as_float(v[j]) + b) * wgt);
+            }
           }
         }
       }
@@ -1111,7 +1152,7 @@ bool pair_mode() {
 // at least two packed-weight stages.
 bool pair_fits(const GemmParams& p, bool gateup) {
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
-  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (gateup ? kEpiStageBytes : 0) + 128;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (gateup ? kEpiStageBytes : kEpiStageDownBytes) + 128;
   const int tokens = 6 * (((p.max_tok + 31) >> 5) << 4) * 128;   // 6 x 64-K or 3 x 128-K slots
   return 227 * 1024 - fixed - scale_tile - tokens >= 2 * kWStageBytes;
 }
@@ -1127,7 +1168,7 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
-  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : 0) + 128;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : kEpiStageDownBytes) + 128;
   // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
   p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
   // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot
