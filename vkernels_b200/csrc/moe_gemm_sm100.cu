@@ -3,7 +3,7 @@
 //
 // Orientation: the WEIGHTS are the M operand. One work item is 128 weight rows
 // (gate/up GEMM: 64 gate rows + the 64 matching up rows; down GEMM: 128 rows)
-// against up to 256 tokens of ONE expert. A thread of a dequant warp owns one
+// against up to 256 tokens of ONE expert (320 for a CTA pair, see below). A thread of a dequant warp owns one
 // weight row = one TMEM lane: it reads the row's packed nibbles (K-contiguous,
 // exactly the memory layout of the weights), expands them to bf16 with the
 // exact table (common.cuh) and stores them with tcgen05.st as the A operand in
@@ -17,14 +17,25 @@
 //   down    : bias, routing weight, red.global.add.f32 into out[token, h]
 //             (the weighted un-permute/combine, fused)
 //
-// Warp roles (512 threads, one persistent CTA per SM):
+// Warp roles (640 threads, one persistent CTA per SM):
 //   warp 0      TMA producer: packed weights (2 boxes of 64 rows x 128 B per
-//               256-K stage), scale bytes (bulk copy per item), token tiles
+//               256-K stage) and scale bytes (bulk copy per item)
 //   warp 1      tcgen05.mma issuer + tensor-memory allocation
-//   warps 4-11  dequant: shared memory -> registers -> tensor memory
-//   warps 12-15 epilogue: tensor memory -> registers -> global
-// Tensor memory (512 columns): 0..255 accumulator, 256..511 eight A stages of
-// 64 K-elements (32 columns each).
+//   warp 2      TMA producer: token tiles
+//   warps 4-15  dequant: shared memory -> registers -> tensor memory (three sets of four)
+//   warps 16-19 epilogue: tensor memory -> registers -> global
+//
+// Two forms, chosen by the largest token tile of the launch:
+//   lone CTA (tiles up to 128 tokens, the decode regime): the stage length grows as the tile
+//     shrinks (256 K-elements up to 64 tokens, 128 up to 128), because the issuer's per-stage
+//     handshake costs a few hundred cycles whatever the stage holds;
+//   CTA pair (larger tiles, the prefill regime): a cluster of two CTAs works on one item of
+//     256 weight rows x up to 320 tokens with cta_group::2 MMAs. Each CTA dequantises its own
+//     128 rows and stages HALF of the token rows, which halves the token bytes an SM pulls
+//     from L2 per flop. Tensor memory: columns 0..255 main accumulator, 256..319 a second
+//     accumulator for tokens 256..319 (fed by a second MMA per K block), 320..511 three A
+//     slots of 128 K-elements. One ring serves A slots and token slots: the token bytes are
+//     expected on the barrier the dequant warps arrive on.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag all
 // roles observe, the CTA frees its tensor memory and returns, and the launcher
@@ -61,9 +72,12 @@ constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per laun
 constexpr int kMaxAStages = 8;
 constexpr int kMaxBStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
-constexpr int kThreads = 512;
+constexpr int kDequantSets = 3;      // dequant warps per tensor-memory lane quarter
+constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
+constexpr int kThreads = (kEpiWarp0 + 4) * 32;
 constexpr int kTmemCols = 512;
-constexpr int kEpiStageBytes = 2 * 32 * 64 * 2;   // gate/up epilogue staging (two rounds)
+constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
+constexpr int kEpiStageBytes = 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds)
 constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
 constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of SM clock
 
@@ -241,6 +255,17 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 32 columns: thread t gets, per group of 8 columns i, rows t / 4 (registers 4i, 4i+1)
+// and t / 4 + 8 (registers 4i+2, 4i+3) at columns 8i + 2 * (t % 4) and the next one.
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -265,14 +290,23 @@ __device__ __forceinline__ bool elect_one() {
 // NaN come out as in the CPU definition: NaN stays NaN (comparisons with NaN
 // are false), +inf gives inf * u, and -inf, where the definition evaluates
 // -inf / inf = NaN, is patched by the final select.
+__device__ __forceinline__ float fmin_nan(float a, float b) {   // NaN if either operand is NaN
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
 __device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
-  if (limit > 0.0f) {   // uniform across the launch
-    g = (g > limit) ? limit : g;
-    u = (u > limit) ? limit : u;
-    u = (u < -limit) ? -limit : u;
+  if (limit > 0.0f) {   // uniform across the launch; a NaN operand stays NaN
+    g = fmin_nan(g, limit);
+    u = fmax_nan(fmin_nan(u, limit), -limit);
   }
   // exp(-g) overflows fp32 beyond 88; the quotient is below 1e-36 in magnitude either way.
-  const float ng = (-g > 87.0f) ? 87.0f : -g;
+  const float ng = fminf(-g, 87.0f);
   const float r = __fdividef(g, 1.0f + __expf(ng));
   return ((g == -INFINITY) ? __int_as_float(0x7FC00000) : r) * u;
 }
@@ -434,7 +468,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   if (tid == 0) {
     for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
-      mbar_init(smem_u32(&bars->w_empty[i]), 8);
+      mbar_init(smem_u32(&bars->w_empty[i]), 4 * kDequantSets);
     }
     for (int i = 0; i < kMaxAStages; ++i) {
       mbar_init(smem_u32(&bars->a_full[i]), kMerged ? 4 * CTAS + 1 : 4);
@@ -443,7 +477,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     for (int i = 0; i < kMaxBStages; ++i) mbar_init(smem_u32(&bars->b_full[i]), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->sc_full[i]), 1);
-      mbar_init(smem_u32(&bars->sc_empty[i]), 8);
+      mbar_init(smem_u32(&bars->sc_empty[i]), 4 * kDequantSets);
     }
     mbar_init(smem_u32(&bars->acc_full), 1);
     mbar_init(smem_u32(&bars->acc_empty), 4 * CTAS);
@@ -719,21 +753,23 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
       acc_phase ^= 1u;
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < kEpiWarp0) {
     // ------------------------------ dequant --------------------------------
-    // Warp (q, h): TMEM lane quarter q; it takes the stages whose running index
-    // has parity h. A stage is decoded 64 K-elements (32 columns) at a time:
+    // Warp (q, h): TMEM lane quarter q; set h takes every kDequantSets-th stage of the
+    // running stage sequence. A stage is decoded 64 K-elements (32 columns) at a time:
     // two 16-byte chunks of the thread's row -> 32 registers -> one tcgen05.st.
     // With 64-K stages the store of a stage stays in flight while the warp's next
     // stage is decoded; longer stages overlap their own pieces instead.
     const int q = warp & 3, h = (warp - 4) >> 2;
     const int row = q * 32 + lane;                 // TMEM lane of this thread
-    // gate/up items interleave the two halves: even lanes hold gate rows, odd
-    // lanes the matching up rows, so the epilogue pairs them with one shuffle.
-    const int srow = GATEUP ? ((row & 1) * 64 + (row >> 1)) : row;   // row inside the staged tile
+    // gate/up items interleave the two halves in groups of 16 lanes: lanes 0-7 of a group hold
+    // the gate rows of eight features, lanes 8-15 the matching up rows, so a 16x256b read of
+    // the accumulator hands one thread the gate and the up value of the same (feature, token).
+    const int srow = GATEUP ? (((row >> 3) & 1) * 64 + (row >> 4) * 8 + (row & 7)) : row;   // row inside the staged tile
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols;
     Ring w, a;
-    uint32_t sc_it = 0, stage_idx = 0;
+    uint32_t sc_it = 0;
+    int turn = 0;   // which dequant set takes the coming stage, running over all items
     int pending = -1;   // A slot whose stores are not yet handed to the MMA issuer
     bool ok = true;
     auto retire = [&]() {
@@ -766,8 +802,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                 (srow & 63) * 128;
         const int k_left = p.K - kw * kWStageK;                       // K elements from this W stage on
         const int n_sub = min(kSubPerW, (k_left + KS - 1) / KS);      // pipeline stages in this W stage
-        for (int j = 0; j < n_sub; ++j, ++stage_idx, a.advance(kAStages)) {
-          if ((stage_idx & 1u) != (uint32_t)h) continue;
+        for (int j = 0; j < n_sub; ++j, turn = (turn + 1 == kDequantSets ? 0 : turn + 1), a.advance(kAStages)) {
+          if (turn != h) continue;
           if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 9)) {
             ok = false;
             break;
@@ -812,10 +848,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       ++sc_it;
     }
     retire();
-  } else if (warp >= 12) {
+  } else if (warp >= kEpiWarp0) {
     // ------------------------------ epilogue -------------------------------
     const int q = warp & 3;
-    const int etid = tid - 12 * 32;  // 0..127 = TMEM lane
+    const int etid = tid - kEpiWarp0 * 32;  // 0..127 = TMEM lane
     uint32_t acc_phase = 0;
     int round = 0;   // gate/up staging buffer parity, running over all items
     for (int item = unit; item < n_items; item += n_units, acc_phase ^= 1u) {
@@ -846,43 +882,44 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         continue;
       }
       if (GATEUP) {
-        // lane 2i holds the gate row, lane 2i+1 the up row of feature i (see the
-        // dequant role). Per 32 columns the pair exchanges halves with one shuffle
-        // each: the even lane finishes tokens 0..15, the odd lane tokens 16..31.
-        const bool odd = lane & 1;
+        // Per 32 token columns the warp reads its two 16-lane groups in the 16x256b shape:
+        // a thread then holds gate and up of (feature lane / 4 [+ 8], tokens 8i + 2 * (lane % 4)
+        // and the next one), so the activation needs no exchange between lanes.
         const bool situ = p.activation == 1;   // uniform across the launch
-        const int feat = f * 64 + q * 16 + (lane >> 1);
-        const float bg = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + feat] : 0.0f;
-        const float bu = p.bias ? p.bias[(size_t)tt.expert * 2 * p.n_feat + p.n_feat + feat] : 0.0f;
+        const int fl = q * 16 + (lane >> 2);   // feature inside the item's 64, first lane group
+        const int tk = (lane & 3) * 2;
+        float bg[2] = {0.f, 0.f}, bu[2] = {0.f, 0.f};
+        if (p.bias) {
+          const float* bp = p.bias + (size_t)tt.expert * 2 * p.n_feat + f * 64 + fl;
+          bg[0] = bp[0]; bg[1] = bp[8]; bu[0] = bp[p.n_feat]; bu[1] = bp[p.n_feat + 8];
+        }
         for (int c0 = 0; c0 < tt.n_rows; c0 += 32, ++round) {
-          uint32_t v[32];
-          tc_ld32(t_lane + c0, v);
+          uint32_t va[16], vb[16];
+          tc_ld_16x256b_x4(t_lane + c0, va);
+          tc_ld_16x256b_x4(t_lane + (16u << 16) + c0, vb);
           tc_wait_ld();
           if (c0 + 32 >= tt.n_rows) release_acc();   // last read of the accumulator
           // which of the round's 32 tokens are real rows: one shared-memory read per lane and
-          // a ballot, so the 16 stores below depend on no load
+          // a ballot, so the stores below depend on no load
           const int my_t = c0 + lane;
           const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_tok[my_t] >= 0);
-          const int tsel = odd ? 16 : 0;
-          // the exchange: 16 shuffles, then g/u of this thread's 16 tokens in registers
-          float gv[16], uv[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t mine = odd ? v[16 + j] : v[j];      // my row, my tokens
-            const uint32_t give = odd ? v[j] : v[16 + j];      // my row, partner's tokens
-            const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, give, 1);
-            gv[j] = __uint_as_float(odd ? got : mine) + bg;
-            uv[j] = __uint_as_float(odd ? mine : got) + bu;
-          }
           // activation -> bf16 into the staging tile [token][feature] of this round ...
-          uint16_t* stg = epi_stage + (round & 1) * (32 * 64) + tsel * 64 + (q * 16 + (lane >> 1));
-          if (!situ) {
+          uint16_t* stg = epi_stage + (round & 1) * (32 * kEpiPitch) + tk * kEpiPitch + fl;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) stg[j * 64] = f32_to_bf16_bits(swiglu_fast(gv[j], uv[j], p.limit));
-          } else {
+          for (int i = 0; i < 4; ++i) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              stg[j * 64] = f32_to_bf16_bits(moe_act_value(1, gv[j], uv[j], p.limit, p.beta, p.linear_beta));
+            for (int e = 0; e < 2; ++e) {
+              const float g0 = __uint_as_float(va[4 * i + e]) + bg[0], u0 = __uint_as_float(va[4 * i + 2 + e]) + bu[0];
+              const float g1 = __uint_as_float(vb[4 * i + e]) + bg[1], u1 = __uint_as_float(vb[4 * i + 2 + e]) + bu[1];
+              uint16_t* d = stg + (8 * i + e) * kEpiPitch;
+              if (!situ) {
+                d[0] = f32_to_bf16_bits(swiglu_fast(g0, u0, p.limit));
+                d[8] = f32_to_bf16_bits(swiglu_fast(g1, u1, p.limit));
+              } else {
+                d[0] = f32_to_bf16_bits(moe_act_value(1, g0, u0, p.limit, p.beta, p.linear_beta));
+                d[8] = f32_to_bf16_bits(moe_act_value(1, g1, u1, p.limit, p.beta, p.linear_beta));
+              }
+            }
           }
           // ... then rows leave as 16-byte pieces: 8 consecutive threads write one 128-byte act row.
           // One barrier per round: a buffer is rewritten two rounds later, after the barrier of
@@ -893,7 +930,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const int piece = etid + i * 128;           // 256 pieces of 16 bytes
             const int tok = piece >> 3, ch = piece & 7;
             if ((real >> tok) & 1u) {
-              const uint4 val = *reinterpret_cast<const uint4*>(epi_stage + (round & 1) * (32 * 64) + tok * 64 + ch * 8);
+              const uint4 val = *reinterpret_cast<const uint4*>(epi_stage + (round & 1) * (32 * kEpiPitch) + tok * kEpiPitch + ch * 8);
               *reinterpret_cast<uint4*>(p.act + (size_t)(tt.row0 + c0 + tok) * p.n_feat + f * 64 + ch * 8) = val;
             }
           }
@@ -1222,11 +1259,7 @@ void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap
                  bool use_pair, cudaStream_t stream) {
   if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
-  else if (use_pair) {
-    static const bool ks64 = [] { const char* e = std::getenv("VK_MOE_PAIR_KS"); return e && std::atoi(e) == 64; }();
-    if (ks64) launch_gemm_ks<GATEUP, 64, 2>(tw, tb, tb64, p, stream);
-    else launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
-  }
+  else if (use_pair) launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
   else launch_gemm_ks<GATEUP, 64, 1>(tw, tb, tb64, p, stream);
 }
 
