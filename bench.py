@@ -199,6 +199,13 @@ def kernel_times(fn, calls):
     return g.value / max(n.value, 1), d.value / max(n.value, 1), n.value
 
 
+# DRAM bytes (read + write) of one launch of the gate/up GEMM, from the ncu capture summarised in
+# profiles/moe_gemm_sm100_c2_prefill_T8192_sections.txt (1.467 TB/s x 1.0246 ms, cold caches).
+# The kernel is tensor-bound; its algorithmic bytes are 1.51 GB (packed weights, scales, token
+# rows in, activation rows out), so every byte crosses HBM once.
+GATEUP_DRAM_BYTES = {("c2_gptoss120b_prefill", 8192): 1.503e9}
+
+
 def launches_per_step(T, slots):
     """Kernels of this library per layer call: router logits + top-k, alignment (1 kernel up to
     1024 routed slots, else 3), tile list, row gather, gate/up GEMM, down GEMM."""
@@ -270,7 +277,8 @@ def run_single_gpu(args, cfg, T):
     roofline = {"bound": "tensor", "kernel": "moe_gemm_sm100_kernel<gate/up>", "achieved": achieved,
                 "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
                 "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
-                "traffic": None, "algorithmic_flops_per_launch": flops_gateup, "ms_per_launch": g_ms,
+                "traffic": GATEUP_DRAM_BYTES.get((cfg.name, T)), "traffic_unit": "bytes",
+                "algorithmic_flops_per_launch": flops_gateup, "ms_per_launch": g_ms,
                 "down_kernel": {"achieved": flops_down / (d_ms * 1e-3) / 1e12, "ms_per_launch": d_ms,
                                 "frac": flops_down / (d_ms * 1e-3) / 1e12 / tensor_peak},
                 "layer": {"achieved": cfg.flops(T) / (ms_per_step * 1e-3) / 1e12,

@@ -191,6 +191,27 @@ def test_prefill_shapes_on_a_token_subsample(name, T, n_sub):
     _parity(cfg, T, impl="tcgen05", tokens=tokens, logits=logits, backend="torch")
 
 
+@pytest.mark.parametrize("n_hot", [129, 256, 257, 272, 300, 320, 321, 400, 641])
+def test_token_tile_edges_of_the_cta_pair_form(n_hot):
+    """One expert receives exactly n_hot tokens: the sizes around the 256-token main accumulator,
+    the 64-token extension (257..320), the split into two items (321+), and a tile just over the
+    lone-CTA limit (129). Every token also visits a second, lightly loaded expert."""
+    cfg = syn.scaled(syn.CONFIGS["c0"], H=512, I=256, E=8, top_k=2)
+    T = max(n_hot + 37, 330)   # more than 256 tokens, so the CTA-pair form is selected
+    w, A, _ = make_case(cfg, T)
+    rng = np.random.default_rng(n_hot)
+    ids = np.empty((T, 2), np.int32)
+    hot = np.zeros(T, bool)
+    hot[rng.choice(T, n_hot, replace=False)] = True
+    ids[:, 0] = np.where(hot, 3, rng.integers(4, 8, T))
+    ids[:, 1] = rng.integers(0, 3, T)
+    tw = rng.random((T, 2), dtype=np.float32)
+    idt, twt = torch.from_numpy(ids).to(DEV), torch.from_numpy(tw).to(DEV)
+    got = to_np(gpu_layer(A, w, idt, twt, impl="tcgen05"))
+    ref = oracle_layer(A, w, idt, twt)
+    assert_close_bf16(got, ref, f"{n_hot} tokens on one expert")
+
+
 def test_c3_shape_with_shared_expert_on_a_token_subsample():
     cfg = syn.CONFIGS["c3"]
     T = 4096   # the full T = 16384 runs in bench.py; the weights (5.7 GB) are full size here
