@@ -344,8 +344,11 @@ def run_multi_gpu(args, cfg, T):
     # this rank's two GEMM kernels (every rank times its own; rank 0 reports its pair)
     layer.count_local_slots = True
     g_ms, d_ms, _ = kernel_times(step, max(3, min(args.steps, 10)))
+    layer.time_phases = True
+    step()
     stats = layer.last_stats()
     layer.count_local_slots = False
+    layer.time_phases = False
     peaks = measured_peaks()
     tensor_peak = peaks["bf16_tflops_sustained"]
     flops_gateup = 4 * stats["local_slots"] * cfg.I * cfg.H

@@ -77,10 +77,13 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
 // every product is exact in fp32. Partial sums over 64 K-elements are formed by
 // mma.sync.m16n8k16 (smallest terms first) and added to the running fp32 totals in
 // registers, which keeps the result within fp32 reassociation noise of a sequential fp32 dot.
-// CTA: 64 tokens x 128 experts, 8 warps as 4 (tokens) x 2 (experts); warp tile 16 x 64.
-constexpr int MT = 64, ME = 128, MK = 64, MPAD = 8;   // +8 bf16 per row: conflict-free ldmatrix
+// CTA: 64 tokens x ME experts (128 or 64), 8 warps as 4 (tokens) x 2 (experts); warp tile
+// 16 x ME / 2. The narrower tile doubles the CTA count (and lets two CTAs share an SM) when the
+// batch alone does not fill the machine.
+constexpr int MT = 64, MK = 64, MPAD = 8;   // +8 bf16 per row: conflict-free ldmatrix
 constexpr int MROW = MK + MPAD;
 
+template <int ME>
 struct RouterSmem {
   uint16_t x[2][MT][MROW];
   uint16_t w[2][3][ME][MROW];
@@ -108,19 +111,22 @@ __device__ __forceinline__ void split3(float w, uint16_t& hi, uint16_t& mid, uin
   lo = f32_to_bf16_bits(r2);
 }
 
+template <int ME>
 __global__ void __launch_bounds__(256)
 router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict__ wr,
                          float* __restrict__ logits, int T, int H, int E) {
+  constexpr int NT = ME / 16;        // 8-expert MMA tiles per warp
+  constexpr int WV = ME / 16;        // float4 loads of the weight tile per thread and chunk
   extern __shared__ __align__(16) uint8_t router_smem_raw[];
-  RouterSmem& sm = *reinterpret_cast<RouterSmem*>(router_smem_raw);
+  RouterSmem<ME>& sm = *reinterpret_cast<RouterSmem<ME>*>(router_smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t0 = blockIdx.x * MT, e0 = blockIdx.y * ME;
-  const int wt = warp & 3, we = warp >> 2;   // warp tile: tokens wt*16.., experts we*64..
+  const int wt = warp & 3, we = warp >> 2;   // warp tile: tokens wt*16.., experts we*(ME/2)..
 
   // global -> register staging of one K chunk: x 64 x 64 bf16 (2 x 16 B per thread),
-  // w 128 x 64 fp32 (8 x 16 B per thread)
+  // w ME x 64 fp32 (ME / 16 x 16 B per thread)
   uint4 xr[2];
-  float4 wv[8];
+  float4 wv[WV];
   auto load_chunk = [&](int k0) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -131,8 +137,8 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
                                : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * 256;           // 0..2047: row = idx / 16, 4 fp32 at (idx % 16) * 4
+    for (int i = 0; i < WV; ++i) {
+      const int idx = tid + i * 256;           // row = idx / 16, 4 fp32 at (idx % 16) * 4
       const int r = idx >> 4, c = (idx & 15) * 4;
       const int e = e0 + r, k = k0 + c;
       wv[i] = (e < E && k < H) ? *reinterpret_cast<const float4*>(wr + (size_t)e * H + k)
@@ -146,7 +152,7 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
       *reinterpret_cast<uint4*>(&sm.x[buf][idx >> 3][(idx & 7) * 8]) = xr[i];
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < WV; ++i) {
       const int idx = tid + i * 256;
       const int r = idx >> 4, c = (idx & 15) * 4;
       const float f[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
@@ -162,9 +168,9 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
     }
   };
 
-  float total[8][4];
+  float total[NT][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n)
+  for (int n = 0; n < NT; ++n)
 #pragma unroll
     for (int j = 0; j < 4; ++j) total[n][j] = 0.0f;
 
@@ -175,9 +181,9 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
   for (int ch = 0; ch < n_chunks; ++ch) {
     const int buf = ch & 1;
     if (ch + 1 < n_chunks) load_chunk((ch + 1) * MK);
-    float part[8][4];
+    float part[NT][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int j = 0; j < 4; ++j) part[n][j] = 0.0f;
 #pragma unroll
@@ -188,10 +194,10 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
 #pragma unroll
       for (int term = 2; term >= 0; --term) {   // lo, mid, hi
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {         // two 8-expert tiles per ldmatrix.x4
+        for (int np = 0; np < NT / 2; ++np) {    // two 8-expert tiles per ldmatrix.x4
           uint32_t b[4];
           // matrices: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
-          const int row = we * 64 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int row = we * (ME / 2) + np * 16 + (lane & 7) + ((lane >> 4) << 3);
           const int col = ks * 16 + ((lane >> 3) & 1) * 8;
           ldmatrix_x4(b, &sm.w[buf][term][row][col]);
           mma_bf16_16816(part[np * 2], a, b[0], b[1]);
@@ -200,7 +206,7 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
       }
     }
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int j = 0; j < 4; ++j) total[n][j] += part[n][j];
     if (ch + 1 < n_chunks) store_chunk(buf ^ 1);
@@ -209,8 +215,8 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
   // c fragment: rows lane / 4 and + 8, columns (lane % 4) * 2 and + 1
   const int r0 = t0 + wt * 16 + (lane >> 2);
 #pragma unroll
-  for (int n = 0; n < 8; ++n) {
-    const int e = e0 + we * 64 + n * 8 + (lane & 3) * 2;
+  for (int n = 0; n < NT; ++n) {
+    const int e = e0 + we * (ME / 2) + n * 8 + (lane & 3) * 2;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int t = r0 + half * 8;
@@ -418,13 +424,22 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
              (reinterpret_cast<uintptr_t>(wr) & 15u) == 0) {
     static bool configured = false;
     if (!configured) {
-      VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)sizeof(RouterSmem)));
+      VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(RouterSmem<128>)));
+      VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(RouterSmem<64>)));
       configured = true;
     }
-    dim3 grid((T + MT - 1) / MT, (E + ME - 1) / ME);
-    router_logits_mma_kernel<<<grid, 256, sizeof(RouterSmem), static_cast<cudaStream_t>(stream)>>>(
-        x, wr, logits, T, H, E);
+    const int t_tiles = (T + MT - 1) / MT;
+    if (t_tiles * ((E + 127) / 128) >= 2 * 148) {
+      dim3 grid(t_tiles, (E + 127) / 128);
+      router_logits_mma_kernel<128><<<grid, 256, sizeof(RouterSmem<128>), static_cast<cudaStream_t>(stream)>>>(
+          x, wr, logits, T, H, E);
+    } else {
+      dim3 grid(t_tiles, (E + 63) / 64);
+      router_logits_mma_kernel<64><<<grid, 256, sizeof(RouterSmem<64>), static_cast<cudaStream_t>(stream)>>>(
+          x, wr, logits, T, H, E);
+    }
   } else {
     dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
     router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, T, H, E);

@@ -95,6 +95,7 @@ class ExpertParallelMoE:
         self.begins = torch.tensor(self.begins_host, dtype=torch.int32, device=self.device)
         self._stats = {}
         self.count_local_slots = False   # last_stats()["local_slots"]: one extra host read per step
+        self.time_phases = False         # last_stats()["phase_ms"]: CUDA events between the phases
 
     @classmethod
     def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
@@ -128,11 +129,21 @@ class ExpertParallelMoE:
         T, H = x.shape
         world, rank, slots = self.world, self.rank, self.slots
         dev = x.device
+        marks = []
+
+        def mark(name):
+            if self.time_phases:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         if topk is None:
             ids, w = self.backend.route(x)
             ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
         else:
             ids, w = topk
+        mark("route")
         # 2. counts
         counts = torch.zeros(world, dtype=torch.int32, device=dev)
         self.backend.pack(x, ids, w, self.n_shared, world, rank, self.begins, counts, None, None, None, None, 0)
@@ -141,6 +152,7 @@ class ExpertParallelMoE:
         both = torch.stack([counts, recv_counts]).cpu()          # the step's one host read
         send_n, recv_n = both[0].tolist(), both[1].tolist()
         R_send, R_recv = sum(send_n), sum(recv_n)
+        mark("counts")
         # 3. pack
         cursor = (torch.cumsum(counts, 0) - counts).to(torch.int32)
         row_of = torch.empty((T, world), dtype=torch.int32, device=dev)
@@ -149,6 +161,7 @@ class ExpertParallelMoE:
         send_w = torch.empty((max(R_send, 1), slots), dtype=torch.float32, device=dev)
         self.backend.pack(x, ids, w, self.n_shared, world, rank, self.begins, cursor, row_of, send_x,
                           send_ids, send_w, 1)
+        mark("pack")
         # 4. dispatch
         recv_x = torch.empty((max(R_recv, 1), H), dtype=x.dtype, device=dev)
         dist.all_to_all_single(recv_x[:R_recv], send_x[:R_send], recv_n, send_n, group=self.group)
@@ -156,22 +169,30 @@ class ExpertParallelMoE:
         recv_w = torch.empty((max(R_recv, 1), slots), dtype=torch.float32, device=dev)
         dist.all_to_all_single(recv_ids[:R_recv], send_ids[:R_send], recv_n, send_n, group=self.group)
         dist.all_to_all_single(recv_w[:R_recv], send_w[:R_send], recv_n, send_n, group=self.group)
+        mark("dispatch")
         # 5. local experts
         if R_recv > 0:
             part = self.backend.experts(recv_x[:R_recv], recv_ids[:R_recv], recv_w[:R_recv])
         else:
             part = torch.zeros((0, H), dtype=torch.float32, device=dev)
+        mark("experts")
         local_slots = int((recv_ids[:R_recv] >= 0).sum()) if self.count_local_slots else None
         # 6. return
         back = torch.empty((max(R_send, 1), H), dtype=torch.float32, device=dev)
         dist.all_to_all_single(back[:R_send], part, send_n, recv_n, group=self.group)
+        mark("return")
         # 7. combine
         out = torch.empty((T, H), dtype=x.dtype, device=dev)
         self.backend.combine(back, row_of, T, H, world, out)
+        mark("combine")
+        phase_ms = None
+        if self.time_phases:
+            torch.cuda.synchronize(dev)
+            phase_ms = {marks[i + 1][0]: round(marks[i][1].elapsed_time(marks[i + 1][1]), 4) for i in range(len(marks) - 1)}
         self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T,
                        "launches_per_step": 2 + 2 + 1 + (1 if R_recv * slots <= 1024 else 3) + 4,
                        "dispatch_bytes": R_send * (H * 2 + slots * 8), "combine_bytes": R_recv * H * 4,
-                       "local_slots": local_slots}
+                       "local_slots": local_slots, "phase_ms": phase_ms}
         return out
 
     __call__ = forward
