@@ -328,6 +328,8 @@ def run_multi_gpu(args, cfg, T):
     dev = f"cuda:{local}"
     dist.init_process_group("nccl", device_id=torch.device(dev))
     layer = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T // world)
+    if os.environ.get("VK_EP_FORM", "peer") == "peer":
+        layer.enable_peer_memory(T // world)   # falls back to the collective form when unavailable
     T_local = T // world
     A = syn.make_activations(cfg, T, backend="torch", device=dev, seed=cfg.seed)[rank * T_local:(rank + 1) * T_local].contiguous()
     step = lambda: layer(A)

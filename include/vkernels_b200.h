@@ -198,6 +198,48 @@ int vk_cuda_moe_ep_pack(const uint16_t* x, const int32_t* topk_ids, const float*
 int vk_cuda_moe_ep_combine(const float* recv_rows, const int32_t* row_of, int T, int H, int world,
                            uint16_t* out_bf16, float* out_f32, void* stream);
 
+/* Peer-memory form of expert parallelism (no reference counterpart: the reference moves token
+ * rows and partial results through its collective, dist_moe.cpp:276-328). Only routing records
+ * travel through the collective; the expert kernels read each token row and add each result in
+ * the home rank's memory, mapped into this process (peer loads and red.global.add over NVLink).
+ *
+ * vk_cuda_moe_ep_pack_meta: like phase 1 of vk_cuda_moe_ep_pack, but writes only
+ *   meta [rows, 1 + 2*(k + n_shared)] int32 = {home token index, local expert id per slot
+ *   (-1 = another rank's), routing weight bits per slot}.
+ * vk_cuda_moe_ep_unpack_meta: received records (grouped by source rank, recv_counts[s] rows from
+ *   rank s) -> ids / w [R, slots] for the local expert call, and per row the address of the
+ *   token's activation row (x_bases[s] + token*H*2) and fp32 output row (out_bases[s] + token*H*4).
+ * vk_cuda_fused_moe_mxfp4_rows: vk_hip_fused_moe_mxfp4 with row address arrays in place of A and
+ *   out (a_rows[m], out_rows[m]: device arrays of M addresses, rows 16-byte aligned). */
+int vk_cuda_moe_ep_pack_meta(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                             int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                             int32_t* meta, void* stream);
+int vk_cuda_moe_ep_unpack_meta(const int32_t* meta, int R, int slots, const int32_t* recv_counts,
+                               int world, const uint64_t* x_bases, const uint64_t* out_bases, int H,
+                               int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
+                               void* stream);
+/* Host-free record exchange: meta_bases[d] / count_bases[d] are the addresses, in this process,
+ * of rank d's receive area (world segments of cap records, one per source rank) and of its
+ * count array (world int32). pack: writes this rank's records for d into segment `rank` of d's
+ * area and then its count into count_bases[d][rank] (cursor [world] zeroed by the caller).
+ * unpack: over all world*cap record slots of the local area; slots past recv_counts[s] become
+ * "not routed" rows (ids -1, w 0). A cross-rank barrier belongs between the two. */
+int vk_cuda_moe_ep_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int T, int k,
+                                  int n_shared, int world, int rank, const int32_t* expert_begin,
+                                  int32_t* cursor, const uint64_t* meta_bases,
+                                  const uint64_t* count_bases, int cap, void* stream);
+int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
+                                    int slots, const uint64_t* x_bases, const uint64_t* out_bases,
+                                    int H, int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
+                                    void* stream);
+int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                                 const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                                 uint16_t* act_scratch, const uint64_t* out_rows, int M, int hidden,
+                                 int ispp, int top_k, const int32_t* sorted_ids,
+                                 const int32_t* expert_ids, int EM, float swiglu_limit, int activation,
+                                 float beta, float linear_beta, const float* b13, const float* b2,
+                                 int block_size, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,8 +73,19 @@ def _worker(rank, world, port, tmp):
         err_oracle = float(np.max(np.abs(got - ref[lo:hi])))
         ok = ok and err_oracle <= 2 ** -6 * scale
         ok = ok and T_local <= stats["rows_sent"] <= T_local * world
+
+        # peer-memory form: same routing, rows read and results added in the home rank's memory
+        peer = ep.enable_peer_memory(T_local)
+        err_peer = -1.0
+        if peer:
+            for _ in range(2):   # twice: the buffers are reused from step to step
+                y2 = ep(A[lo:hi].contiguous())
+            torch.cuda.synchronize()
+            err_peer = float(np.max(np.abs(y2.float().cpu().numpy() - want)))
+            ok = ok and err_peer <= 2 ** -7 * scale and ep.last_stats()["form"] == "peer memory"
         open(os.path.join(tmp, f"rank{rank}.txt"), "w").write(
-            f"{int(ok)} err_single={err_single} err_oracle={err_oracle} scale={scale} {stats}")
+            f"{int(ok)} err_single={err_single} err_oracle={err_oracle} peer={peer} err_peer={err_peer} "
+            f"scale={scale} {stats} {ep.last_stats()}")
     finally:
         dist.destroy_process_group()
 

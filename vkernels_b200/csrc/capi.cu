@@ -25,6 +25,22 @@ void ep_launch_pack(const uint16_t* x, const int32_t* topk_ids, const float* top
                     float* send_w, int phase, cudaStream_t stream);
 void ep_launch_combine(const float* recv_rows, const int32_t* row_of, int T, int H, int world,
                        uint16_t* out_bf16, float* out_f32, cudaStream_t stream);
+void ep_launch_pack_meta(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                         int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                         int32_t* meta, cudaStream_t stream);
+void ep_launch_unpack_meta(const int32_t* meta, int R, int slots, const int32_t* recv_counts, int world,
+                           const unsigned long long* x_bases, const unsigned long long* out_bases,
+                           int H, int32_t* ids, float* w, unsigned long long* a_rows,
+                           unsigned long long* out_rows, cudaStream_t stream);
+void ep_launch_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                              int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                              const unsigned long long* meta_bases, const unsigned long long* count_bases,
+                              int cap, cudaStream_t stream);
+void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
+                                int slots, const unsigned long long* x_bases,
+                                const unsigned long long* out_bases, int H, int32_t* ids, float* w,
+                                unsigned long long* a_rows, unsigned long long* out_rows,
+                                cudaStream_t stream);
 }  // namespace vkernels::kernels::cuda
 
 enum { VK_OK = 0, VK_ERROR_INVALID_ARGUMENT = 1, VK_ERROR_OUT_OF_RANGE = 2,
@@ -230,6 +246,70 @@ int vk_cuda_moe_ep_combine(const float* recv_rows, const int32_t* row_of, int T,
   VK_TRY
   vkc::ep_launch_combine(recv_rows, row_of, T, H, world, out_bf16, out_f32,
                          static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_pack_meta(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                             int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                             int32_t* meta, void* stream) {
+  VK_TRY
+  vkc::ep_launch_pack_meta(topk_ids, topk_w, T, k, n_shared, world, rank, expert_begin, cursor, meta,
+                           static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_unpack_meta(const int32_t* meta, int R, int slots, const int32_t* recv_counts,
+                               int world, const uint64_t* x_bases, const uint64_t* out_bases, int H,
+                               int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
+                               void* stream) {
+  VK_TRY
+  vkc::ep_launch_unpack_meta(meta, R, slots, recv_counts, world,
+                             reinterpret_cast<const unsigned long long*>(x_bases),
+                             reinterpret_cast<const unsigned long long*>(out_bases), H, ids, w,
+                             reinterpret_cast<unsigned long long*>(a_rows),
+                             reinterpret_cast<unsigned long long*>(out_rows),
+                             static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int T, int k,
+                                  int n_shared, int world, int rank, const int32_t* expert_begin,
+                                  int32_t* cursor, const uint64_t* meta_bases,
+                                  const uint64_t* count_bases, int cap, void* stream) {
+  VK_TRY
+  vkc::ep_launch_pack_meta_peer(topk_ids, topk_w, T, k, n_shared, world, rank, expert_begin, cursor,
+                                reinterpret_cast<const unsigned long long*>(meta_bases),
+                                reinterpret_cast<const unsigned long long*>(count_bases), cap,
+                                static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
+                                    int slots, const uint64_t* x_bases, const uint64_t* out_bases,
+                                    int H, int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
+                                    void* stream) {
+  VK_TRY
+  vkc::ep_launch_unpack_meta_peer(meta, recv_counts, world, cap, slots,
+                                  reinterpret_cast<const unsigned long long*>(x_bases),
+                                  reinterpret_cast<const unsigned long long*>(out_bases), H, ids, w,
+                                  reinterpret_cast<unsigned long long*>(a_rows),
+                                  reinterpret_cast<unsigned long long*>(out_rows),
+                                  static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                                 const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                                 uint16_t* act_scratch, const uint64_t* out_rows, int M, int hidden,
+                                 int ispp, int top_k, const int32_t* sorted_ids,
+                                 const int32_t* expert_ids, int EM, float swiglu_limit, int activation,
+                                 float beta, float linear_beta, const float* b13, const float* b2,
+                                 int block_size, void* stream) {
+  VK_TRY
+  vkc::fused_moe_mxfp4_rows(reinterpret_cast<const uint16_t* const*>(a_rows), w13, w13_scale, w2, w2_scale,
+                            topk_w, act_scratch, reinterpret_cast<float* const*>(out_rows), M, hidden,
+                            ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta,
+                            linear_beta, b13, b2, block_size, stream);
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 

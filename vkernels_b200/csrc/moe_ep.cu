@@ -100,6 +100,147 @@ ep_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ ro
   }
 }
 
+// Routing records for the peer-memory form of expert parallelism: nothing but the routing
+// travels through the collective; the token rows themselves are read (and the results added)
+// directly in the home rank's memory by the expert kernels.
+// meta row (1 + 2 * slots int32): home token index, local expert id per slot (-1 = not this
+// rank's), routing weight bits per slot. One thread per token; cursor as in ep_pack phase 1.
+__global__ void __launch_bounds__(256)
+ep_pack_meta_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_w, int T,
+                    int k, int n_shared, int world, int rank, const int32_t* __restrict__ expert_begin,
+                    int32_t* __restrict__ cursor, int32_t* __restrict__ meta) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int slots = k + n_shared, stride = 1 + 2 * slots;
+  unsigned need = n_shared > 0 ? (1u << rank) : 0u;
+  for (int j = 0; j < k; ++j) {
+    const int e = topk_ids[(size_t)t * k + j];
+    if (e >= 0 && e < expert_begin[world]) need |= 1u << owner_rank(e, expert_begin, world);
+  }
+  for (int d = 0; d < world; ++d) {
+    if (!((need >> d) & 1u)) continue;
+    const int row = atomicAdd(&cursor[d], 1);
+    int32_t* m = meta + (size_t)row * stride;
+    m[0] = t;
+    const int b = expert_begin[d], e_end = expert_begin[d + 1];
+    for (int j = 0; j < slots; ++j) {
+      int id = -1;
+      float w = 0.0f;
+      if (j < k) {
+        const int e = topk_ids[(size_t)t * k + j];
+        if (e >= b && e < e_end) {
+          id = e - b;
+          w = topk_w[(size_t)t * k + j];
+        }
+      } else if (d == rank) {
+        id = (e_end - b) + (j - k);
+        w = 1.0f;
+      }
+      m[1 + j] = id;
+      m[1 + slots + j] = __float_as_int(w);
+    }
+  }
+}
+
+// Received records -> routing arrays of the local expert call plus, per received row, the
+// address of the token's activation row and of its fp32 output row in the home rank's memory.
+// Rows arrive grouped by source rank: recv_counts[s] rows from rank s, in rank order.
+__global__ void __launch_bounds__(256)
+ep_unpack_meta_kernel(const int32_t* __restrict__ meta, int R, int slots,
+                      const int32_t* __restrict__ recv_counts, int world,
+                      const unsigned long long* __restrict__ x_bases,
+                      const unsigned long long* __restrict__ out_bases, int H,
+                      int32_t* __restrict__ ids, float* __restrict__ w,
+                      unsigned long long* __restrict__ a_rows, unsigned long long* __restrict__ out_rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  int src = 0, first = 0;
+  for (; src < world - 1; ++src) {
+    const int n = recv_counts[src];
+    if (r < first + n) break;
+    first += n;
+  }
+  const int32_t* m = meta + (size_t)r * (1 + 2 * slots);
+  const unsigned long long tok = (unsigned long long)m[0];
+  a_rows[r] = x_bases[src] + tok * (unsigned long long)H * sizeof(uint16_t);
+  out_rows[r] = out_bases[src] + tok * (unsigned long long)H * sizeof(float);
+  for (int j = 0; j < slots; ++j) {
+    ids[(size_t)r * slots + j] = m[1 + j];
+    w[(size_t)r * slots + j] = __int_as_float(m[1 + slots + j]);
+  }
+}
+
+// Host-free variant of the two kernels above: every rank owns a receive area of `world`
+// segments of `cap` records (one per source rank) in memory all ranks can address. A source
+// writes its records for rank d straight into its segment of d's area (peer stores) and then
+// publishes how many it wrote; no collective call and no host read is needed, and the expert
+// call afterwards runs over all world * cap record slots, the unused ones marked as not routed.
+__global__ void __launch_bounds__(256)
+ep_pack_meta_peer_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_w, int T,
+                         int k, int n_shared, int world, int rank,
+                         const int32_t* __restrict__ expert_begin, int32_t* __restrict__ cursor,
+                         const unsigned long long* __restrict__ meta_bases, int cap) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int slots = k + n_shared, stride = 1 + 2 * slots;
+  unsigned need = n_shared > 0 ? (1u << rank) : 0u;
+  for (int j = 0; j < k; ++j) {
+    const int e = topk_ids[(size_t)t * k + j];
+    if (e >= 0 && e < expert_begin[world]) need |= 1u << owner_rank(e, expert_begin, world);
+  }
+  for (int d = 0; d < world; ++d) {
+    if (!((need >> d) & 1u)) continue;
+    const int row = atomicAdd(&cursor[d], 1);
+    if (row >= cap) continue;   // cannot happen: a token sends at most one record per rank
+    int32_t* m = reinterpret_cast<int32_t*>(meta_bases[d]) + ((size_t)rank * cap + row) * stride;
+    m[0] = t;
+    const int b = expert_begin[d], e_end = expert_begin[d + 1];
+    for (int j = 0; j < slots; ++j) {
+      int id = -1;
+      float w = 0.0f;
+      if (j < k) {
+        const int e = topk_ids[(size_t)t * k + j];
+        if (e >= b && e < e_end) {
+          id = e - b;
+          w = topk_w[(size_t)t * k + j];
+        }
+      } else if (d == rank) {
+        id = (e_end - b) + (j - k);
+        w = 1.0f;
+      }
+      m[1 + j] = id;
+      m[1 + slots + j] = __float_as_int(w);
+    }
+  }
+}
+
+__global__ void ep_publish_counts_kernel(const int32_t* __restrict__ cursor,
+                                         const unsigned long long* __restrict__ count_bases, int world,
+                                         int rank) {
+  const int d = threadIdx.x;
+  if (d < world) reinterpret_cast<int32_t*>(count_bases[d])[rank] = cursor[d];
+}
+
+__global__ void __launch_bounds__(256)
+ep_unpack_meta_peer_kernel(const int32_t* __restrict__ meta, const int32_t* __restrict__ recv_counts,
+                           int world, int cap, int slots, const unsigned long long* __restrict__ x_bases,
+                           const unsigned long long* __restrict__ out_bases, int H,
+                           int32_t* __restrict__ ids, float* __restrict__ w,
+                           unsigned long long* __restrict__ a_rows, unsigned long long* __restrict__ out_rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= world * cap) return;
+  const int src = r / cap, i = r - src * cap;
+  const bool valid = i < recv_counts[src];
+  const int32_t* m = meta + (size_t)r * (1 + 2 * slots);
+  const unsigned long long tok = valid ? (unsigned long long)m[0] : 0ull;
+  a_rows[r] = x_bases[src] + tok * (unsigned long long)H * sizeof(uint16_t);
+  out_rows[r] = out_bases[src] + tok * (unsigned long long)H * sizeof(float);
+  for (int j = 0; j < slots; ++j) {
+    ids[(size_t)r * slots + j] = valid ? m[1 + j] : -1;
+    w[(size_t)r * slots + j] = valid ? __int_as_float(m[1 + slots + j]) : 0.0f;
+  }
+}
+
 // out[r, k] = dequantised weight (bf16 bits); one thread per 8 elements.
 __global__ void __launch_bounds__(256)
 dequant_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
@@ -131,6 +272,64 @@ void ep_launch_pack(const uint16_t* x, const int32_t* topk_ids, const float* top
   ep_pack_kernel<<<(T + 7) / 8, 256, 0, stream>>>(x, topk_ids, topk_w, T, H, k, n_shared, world,
                                                   rank, expert_begin, cursor, row_of, send_x,
                                                   send_ids, send_w, phase);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void ep_launch_pack_meta(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                         int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                         int32_t* meta, cudaStream_t stream) {
+  expects(T >= 0 && k > 0 && n_shared >= 0, "ep_pack_meta: bad dimensions");
+  expects(world >= 1 && world <= 32 && rank >= 0 && rank < world, "ep_pack_meta: bad world/rank");
+  if (T == 0) return;
+  expects(topk_ids && topk_w && expert_begin && cursor && meta, "ep_pack_meta: null buffer");
+  ep_pack_meta_kernel<<<(T + 255) / 256, 256, 0, stream>>>(topk_ids, topk_w, T, k, n_shared, world, rank,
+                                                           expert_begin, cursor, meta);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void ep_launch_unpack_meta(const int32_t* meta, int R, int slots, const int32_t* recv_counts, int world,
+                           const unsigned long long* x_bases, const unsigned long long* out_bases,
+                           int H, int32_t* ids, float* w, unsigned long long* a_rows,
+                           unsigned long long* out_rows, cudaStream_t stream) {
+  expects(R >= 0 && slots > 0 && world >= 1 && world <= 32 && H > 0 && H % 8 == 0,
+          "ep_unpack_meta: bad dimensions");
+  if (R == 0) return;
+  expects(meta && recv_counts && x_bases && out_bases && ids && w && a_rows && out_rows,
+          "ep_unpack_meta: null buffer");
+  ep_unpack_meta_kernel<<<(R + 255) / 256, 256, 0, stream>>>(meta, R, slots, recv_counts, world, x_bases,
+                                                             out_bases, H, ids, w, a_rows, out_rows);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void ep_launch_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int T, int k, int n_shared,
+                              int world, int rank, const int32_t* expert_begin, int32_t* cursor,
+                              const unsigned long long* meta_bases, const unsigned long long* count_bases,
+                              int cap, cudaStream_t stream) {
+  expects(T >= 0 && k > 0 && n_shared >= 0 && cap >= T, "ep_pack_meta_peer: bad dimensions");
+  expects(world >= 1 && world <= 32 && rank >= 0 && rank < world, "ep_pack_meta_peer: bad world/rank");
+  expects(expert_begin && cursor && meta_bases && count_bases, "ep_pack_meta_peer: null buffer");
+  if (T > 0) {
+    expects(topk_ids && topk_w, "ep_pack_meta_peer: null buffer");
+    ep_pack_meta_peer_kernel<<<(T + 255) / 256, 256, 0, stream>>>(topk_ids, topk_w, T, k, n_shared, world,
+                                                                  rank, expert_begin, cursor, meta_bases, cap);
+  }
+  ep_publish_counts_kernel<<<1, 32, 0, stream>>>(cursor, count_bases, world, rank);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
+                                int slots, const unsigned long long* x_bases,
+                                const unsigned long long* out_bases, int H, int32_t* ids, float* w,
+                                unsigned long long* a_rows, unsigned long long* out_rows,
+                                cudaStream_t stream) {
+  expects(cap > 0 && slots > 0 && world >= 1 && world <= 32 && H > 0 && H % 8 == 0,
+          "ep_unpack_meta_peer: bad dimensions");
+  expects(meta && recv_counts && x_bases && out_bases && ids && w && a_rows && out_rows,
+          "ep_unpack_meta_peer: null buffer");
+  const int n = world * cap;
+  ep_unpack_meta_peer_kernel<<<(n + 255) / 256, 256, 0, stream>>>(meta, recv_counts, world, cap, slots,
+                                                                  x_bases, out_bases, H, ids, w, a_rows,
+                                                                  out_rows);
   VK_CUDA_CHECK(cudaGetLastError());
 }
 

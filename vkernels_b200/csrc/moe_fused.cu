@@ -22,7 +22,8 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
                       int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                       float swiglu_limit, int activation, float beta, float linear_beta,
-                      const float* b13, const float* b2, int block_size, cudaStream_t stream);
+                      const float* b13, const float* b2, int block_size, cudaStream_t stream,
+                      const RowPtrs* rows);
 size_t sm100_workspace_bytes(int EM, int hidden, int ispp);
 
 // ---------------------------------------------------------------------------
@@ -95,7 +96,7 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
                float* out, int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
                const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
                float linear_beta, const float* b13, const float* b2, int block_size, bool kmajor,
-               void* stream) {
+               void* stream, const RowPtrs* rows = nullptr) {
   expects(!kmajor, "fused_moe_mxfp4: the K-major weight layout is not supported");
   expects(M >= 0 && EM >= 0 && top_k > 0, "fused_moe_mxfp4: bad M / EM / top_k");
   expects(hidden > 0 && hidden % 64 == 0, "fused_moe_mxfp4: hidden must be a multiple of 64");
@@ -106,9 +107,14 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
   expects(activation == kSwiGLU || activation == kSiTU, "fused_moe_mxfp4: unknown activation");
   expects((long long)M * top_k < (1ll << 30), "fused_moe_mxfp4: M*top_k too large");
   if (M == 0 || EM == 0) return;
-  expects(A && w13 && w13_scale && w2 && w2_scale && topk_w && act_scratch && out &&
-              sorted_ids && expert_ids,
+  expects(w13 && w13_scale && w2 && w2_scale && topk_w && act_scratch && sorted_ids && expert_ids,
           "fused_moe_mxfp4: buffers must not be null");
+  if (rows != nullptr) {
+    expects(rows->a_rows && rows->out_rows, "fused_moe_mxfp4_rows: row address arrays must not be null");
+    expects(get_moe_impl() == MoeImpl::kTcgen05, "fused_moe_mxfp4_rows: only the tcgen05 path takes row addresses");
+  } else {
+    expects(A && out, "fused_moe_mxfp4: buffers must not be null");
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (get_moe_impl() == MoeImpl::kSimt)
     launch_moe_simt(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M, hidden,
@@ -117,9 +123,21 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
   else
     launch_moe_sm100(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M,
                      hidden, ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation,
-                     beta, linear_beta, b13, b2, block_size, s);
+                     beta, linear_beta, b13, b2, block_size, s, rows);
 }
 }  // namespace
+
+void fused_moe_mxfp4_rows(const uint16_t* const* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                          const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                          uint16_t* act_scratch, float* const* out_rows, int M, int hidden, int ispp,
+                          int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                          float swiglu_limit, int activation, float beta, float linear_beta,
+                          const float* b13, const float* b2, int block_size, void* stream) {
+  const RowPtrs rows{a_rows, out_rows};
+  run_fused(nullptr, w13, w13_scale, w2, w2_scale, topk_w, 0, act_scratch, nullptr, M, hidden, ispp,
+            top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2,
+            block_size, false, stream, &rows);
+}
 
 void fused_moe_mxfp4(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
                      const uint8_t* w2, const uint8_t* w2_scale, const int32_t* /*topk_ids*/,

@@ -59,6 +59,21 @@ void fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13, const uint8
                               int activation, float beta, float linear_beta, const float* b13,
                               const float* b2, int block_size, void* stream);
 
+// Row addresses instead of base pointers: token m's activation row is read at a_rows[m] and
+// its result is added at out_rows[m] (hidden bf16 / fp32 values each, 16-byte aligned). The rows
+// may live in another GPU's memory mapped into this process (peer loads and reductions over
+// NVLink): under expert parallelism this is the dispatch and the combine. tcgen05 path only.
+struct RowPtrs {
+  const uint16_t* const* a_rows;
+  float* const* out_rows;
+};
+void fused_moe_mxfp4_rows(const uint16_t* const* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                          const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                          uint16_t* act_scratch, float* const* out_rows, int M, int hidden, int ispp,
+                          int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                          float swiglu_limit, int activation, float beta, float linear_beta,
+                          const float* b13, const float* b2, int block_size, void* stream);
+
 // Device alignment, any N = M*top_k (the reference stops at 1024). Output is
 // bit-identical to the host `moe_align_block_size`: experts ascending, flat
 // index ascending inside an expert, each expert padded to block_size with N,

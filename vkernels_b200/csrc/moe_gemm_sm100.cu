@@ -95,6 +95,7 @@ struct GemmParams {
   const int32_t* sorted_ids;  // [EM]
   uint16_t* act;              // gate/up output [EM, n_feat]
   float* out;                 // down output [M, n_feat]
+  float* const* out_rows;     // optional: address of each token's output row (may be another GPU's memory)
   const TokTile* tiles;
   const int* n_tiles;
   int* status;                // device status word (0 = ok)
@@ -404,7 +405,9 @@ struct Barriers {
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
   int abort_flag;
-  int tile_tok[kPairMaxTok];
+  // per token column of the current item: gate/up 1 for a real row, 0 for padding;
+  // down: address of the token's output row, 0 for padding
+  unsigned long long tile_ref[kPairMaxTok];
   float tile_w[kPairMaxTok];
 };
 
@@ -862,7 +865,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       for (int j = etid; j < tt.n_rows; j += 128) {
         const int flat = p.sorted_ids[tt.row0 + j];
         const bool real = flat >= 0 && flat < p.N;
-        bars->tile_tok[j] = real ? (GATEUP ? 1 : flat / p.top_k) : -1;
+        if (GATEUP) {
+          bars->tile_ref[j] = real ? 1ull : 0ull;
+        } else {
+          const int token = real ? flat / p.top_k : 0;
+          float* orow = p.out_rows ? p.out_rows[token] : p.out + (size_t)token * p.n_feat;
+          bars->tile_ref[j] = real ? reinterpret_cast<unsigned long long>(orow) : 0ull;
+        }
         if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
       named_bar_sync(1, 128);
@@ -902,7 +911,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           // which of the round's 32 tokens are real rows: one shared-memory read per lane and
           // a ballot, so the stores below depend on no load
           const int my_t = c0 + lane;
-          const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_tok[my_t] >= 0);
+          const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_ref[my_t] != 0ull);
           // activation -> bf16 into the staging tile [token][feature] of this round ...
           uint16_t* stg = epi_stage + (round & 1) * (32 * kEpiPitch) + tk * kEpiPitch + fl;
 #pragma unroll
@@ -961,11 +970,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             for (int i = 0; i < 8; ++i) {
               const int tl = (lane >> 3) + 4 * i;
               const int t = c0 + tl;
-              const int token = t < tt.n_rows ? bars->tile_tok[t] : -1;
-              if (token >= 0 && quad_ok) {
+              float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
+              if (orow != nullptr && quad_ok) {
                 const float wgt = bars->tile_w[t];
                 const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
-                red_add_v4(p.out + (size_t)token * p.n_feat + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
+                red_add_v4(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
                            (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
               }
             }
@@ -979,17 +988,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             tc_ld32(t_lane + c0, v);
             tc_wait_ld();
             if (c0 + 32 >= tt.n_rows) release_acc();
-            // lane l keeps token and routing weight of column c0 + l; the loop broadcasts them by
-            // shuffle, so no reduction below waits on a shared-memory load
-            const int my_t = c0 + lane;
-            const int my_tok = my_t < tt.n_rows ? bars->tile_tok[my_t] : -1;
-            const float my_w = my_t < tt.n_rows ? bars->tile_w[my_t] : 0.0f;
-#pragma unroll
+#pragma unroll 4
             for (int j = 0; j < 32; ++j) {
-              const int token = __shfl_sync(0xFFFFFFFFu, my_tok, j);
-              const float wgt = __shfl_sync(0xFFFFFFFFu, my_w, j);
-              if (token >= 0 && row_ok)
-                atomicAdd(p.out + (size_t)token * p.n_feat + hcol, (__uint_as_float(v[j]) + b) * wgt);
+              const int t = c0 + j;
+              float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
+              if (orow != nullptr && row_ok)
+                atomicAdd(orow + hcol, (__uint_as_float(v[j]) + b) * bars->tile_w[t]);
             }
           }
         }
@@ -1069,9 +1073,11 @@ build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int blo
   if (tid == 0) *n_tiles = min(base, max_tiles);
 }
 
-// A_sorted[r, :] = A[sorted_ids[r] / top_k, :] for real rows, zeros otherwise.
+// A_sorted[r, :] = A[sorted_ids[r] / top_k, :] (or the row at A_rows[sorted_ids[r] / top_k]) for
+// real rows, zeros otherwise.
 __global__ void __launch_bounds__(256)
-gather_rows_kernel(const uint16_t* __restrict__ A, const int32_t* __restrict__ sorted_ids,
+gather_rows_kernel(const uint16_t* __restrict__ A, const uint16_t* const* __restrict__ A_rows,
+                   const int32_t* __restrict__ sorted_ids,
                    const int32_t* __restrict__ expert_ids, int block_size, int EM, int N, int top_k,
                    int H, uint16_t* __restrict__ dst) {
   const int vec_per_row = H / 8;  // 16-byte vectors
@@ -1083,7 +1089,10 @@ gather_rows_kernel(const uint16_t* __restrict__ A, const int32_t* __restrict__ s
     if (expert_ids[r / block_size] < 0) continue;  // never read by any tile
     const int flat = sorted_ids[r];
     const bool real = flat >= 0 && flat < N;
-    const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)(real ? flat / top_k : 0) * H);
+    const int token = real ? flat / top_k : 0;
+    // a row address from A_rows may lie in another GPU's memory (peer load over NVLink)
+    const uint4* src = reinterpret_cast<const uint4*>(
+        A_rows != nullptr ? (real ? A_rows[token] : nullptr) : A + (size_t)token * H);
     uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * H);
     for (int i = threadIdx.x; i < vec_per_row; i += 256)
       d[i] = real ? src[i] : make_uint4(0u, 0u, 0u, 0u);
@@ -1339,8 +1348,11 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
                       int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                       float swiglu_limit, int activation, float beta, float linear_beta,
-                      const float* b13, const float* b2, int block_size, cudaStream_t stream) {
+                      const float* b13, const float* b2, int block_size, cudaStream_t stream,
+                      const RowPtrs* rows) {
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const uint16_t* const* a_rows = rows ? rows->a_rows : nullptr;
+  float* const* out_rows = rows ? rows->out_rows : nullptr;
   expects(aligned16(A) && aligned16(w13) && aligned16(w13_scale) && aligned16(w2) &&
               aligned16(w2_scale) && aligned16(act_scratch),
           "fused_moe_mxfp4: A, weights, scales and act_scratch must be 16-byte aligned");
@@ -1371,7 +1383,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   if (!use_pair && max_tok > kMaxTok) max_tok = kMaxTok;
   build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                              n_tiles, max_tok_tiles(EM));
-  gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, sorted_ids, expert_ids, block_size, EM,
+  gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM,
                                                        M * top_k, top_k, hidden, gathered);
 
   GemmParams g{};
@@ -1395,7 +1407,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   }
   {  // down + combine
     GemmParams p = g;
-    p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out;
+    p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out; p.out_rows = out_rows;
     p.K = ispp; p.n_feat = hidden; p.n_ftiles = (hidden + 127) / 128;
     const CUtensorMap tw = make_map(w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ispp / 2, w13_rows_cap,
                                     ispp / 2, 128, 64);

@@ -21,6 +21,16 @@ outputs (dist_moe.cpp:276-328); the sum over ranks computed here is the same qua
 tests check it against that function. Always-on shared experts are replicated: each rank applies
 them to its own tokens as extra local experts after its routed ones.
 
+Peer-memory form (``ExpertParallelMoE.enable_peer_memory``, CUDA only): steps 3-7 shrink to an
+exchange of routing records. Every rank keeps its activations and an fp32 output buffer in
+symmetric memory (``torch.distributed._symmetric_memory``: each rank's buffer is mapped into every
+other rank's address space); the row gather of the expert kernels reads a token's row where it
+lives (peer loads over NVLink) and the down-GEMM epilogue adds its result into the home rank's
+output row (``red.global.add.v4.f32`` over NVLink). Dispatch and combine are thereby fused into
+the two kernels that needed the data anyway; two cross-rank barriers bracket the expert kernels
+(inputs written and outputs zeroed before; all additions done after). If symmetric memory cannot
+be set up the layer stays on the collective form above.
+
 The device-side steps are reached through a small ``backend`` object so the exchange logic can be
 exercised on CPU ranks (gloo) with a stand-in backend; the default backend calls the CUDA library
 and has no CPU path.
@@ -72,6 +82,42 @@ class CudaBackend:
         """fp32 [R, H]: the local experts applied to received rows."""
         return self.layer.experts_fp32(rows, ids, w)
 
+    def pack_meta(self, ids, w, n_shared, world, rank, begins, cursor, meta):
+        T = ids.shape[0]
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_pack_meta(
+                ids.data_ptr(), w.data_ptr(), T, ids.shape[1], n_shared, world, rank, begins.data_ptr(),
+                cursor.data_ptr(), meta.data_ptr(), self._stream())
+        nr.check(rc, "ep_pack_meta")
+
+    def unpack_meta(self, meta, R, slots, recv_counts, world, x_bases, out_bases, H, ids, w, a_rows, out_rows):
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_unpack_meta(
+                meta.data_ptr(), R, slots, recv_counts.data_ptr(), world, x_bases.data_ptr(),
+                out_bases.data_ptr(), H, ids.data_ptr(), w.data_ptr(), a_rows.data_ptr(),
+                out_rows.data_ptr(), self._stream())
+        nr.check(rc, "ep_unpack_meta")
+
+    def pack_meta_peer(self, ids, w, n_shared, world, rank, begins, cursor, meta_bases, count_bases, cap):
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_pack_meta_peer(
+                ids.data_ptr(), w.data_ptr(), ids.shape[0], ids.shape[1], n_shared, world, rank,
+                begins.data_ptr(), cursor.data_ptr(), meta_bases.data_ptr(), count_bases.data_ptr(), cap,
+                self._stream())
+        nr.check(rc, "ep_pack_meta_peer")
+
+    def unpack_meta_peer(self, meta, recv_counts, world, cap, slots, x_bases, out_bases, H, ids, w, a_rows,
+                         out_rows):
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_unpack_meta_peer(
+                meta.data_ptr(), recv_counts.data_ptr(), world, cap, slots, x_bases.data_ptr(),
+                out_bases.data_ptr(), H, ids.data_ptr(), w.data_ptr(), a_rows.data_ptr(),
+                out_rows.data_ptr(), self._stream())
+        nr.check(rc, "ep_unpack_meta_peer")
+
+    def experts_rows(self, a_rows, out_rows, ids, w):
+        self.layer.experts_rows(a_rows, out_rows, ids, w)
+
     def combine(self, back_rows, row_of, T, H, world, out):
         with torch.cuda.device(self.device):
             rc = nr.load_library().vk_cuda_moe_ep_combine(back_rows.data_ptr(), row_of.data_ptr(), T, H, world,
@@ -96,6 +142,7 @@ class ExpertParallelMoE:
         self._stats = {}
         self.count_local_slots = False   # last_stats()["local_slots"]: one extra host read per step
         self.time_phases = False         # last_stats()["phase_ms"]: CUDA events between the phases
+        self._peer = None                # symmetric buffers of the peer-memory form
 
     @classmethod
     def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
@@ -123,9 +170,116 @@ class ExpertParallelMoE:
     def last_stats(self) -> dict:
         return dict(self._stats)
 
+    def enable_peer_memory(self, max_tokens: int) -> bool:
+        """Sets up the peer-memory form for up to ``max_tokens`` local tokens per call. Collective:
+        every rank of the group must call it. Returns False (and leaves the layer on the collective
+        form) when symmetric memory is unavailable on any rank."""
+        ok, err = 1, ""
+        peer = None
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            H = self.hidden
+            x_sym = symm.empty((max_tokens, H), dtype=torch.bfloat16, device=self.device)
+            out_sym = symm.empty((max_tokens, H), dtype=torch.float32, device=self.device)
+            stride = 1 + 2 * self.slots
+            meta_sym = symm.empty((self.world * max_tokens, stride), dtype=torch.int32, device=self.device)
+            cnt_sym = symm.empty((32,), dtype=torch.int32, device=self.device)
+            hx = symm.rendezvous(x_sym, group)
+            ho = symm.rendezvous(out_sym, group)
+            hm = symm.rendezvous(meta_sym, group)
+            hc = symm.rendezvous(cnt_sym, group)
+            dev_ptrs = lambda h: torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=self.device)
+            n_rows = self.world * max_tokens
+            peer = {"x": x_sym, "out": out_sym, "meta": meta_sym, "cnt": cnt_sym, "hx": hx, "ho": ho,
+                    "x_bases": dev_ptrs(hx), "out_bases": dev_ptrs(ho), "meta_bases": dev_ptrs(hm),
+                    "cnt_bases": dev_ptrs(hc), "max_tokens": max_tokens,
+                    # routing arrays and row addresses of the expert call, one per record slot
+                    "ids": torch.empty((n_rows, self.slots), dtype=torch.int32, device=self.device),
+                    "w": torch.empty((n_rows, self.slots), dtype=torch.float32, device=self.device),
+                    "a_rows": torch.empty(n_rows, dtype=torch.int64, device=self.device),
+                    "out_rows": torch.empty(n_rows, dtype=torch.int64, device=self.device),
+                    "cursor": torch.zeros(self.world, dtype=torch.int32, device=self.device)}
+        except Exception as e:  # noqa: BLE001 - any failure means "not available here"
+            ok, err = 0, f"{type(e).__name__}: {e}"
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 1:
+            self._peer = peer
+            return True
+        self._peer = None
+        self._stats["peer_memory_error"] = err
+        return False
+
+    def _forward_peer(self, x: torch.Tensor, topk=None) -> torch.Tensor:
+        T, H = x.shape
+        world, rank, slots = self.world, self.rank, self.slots
+        dev = x.device
+        peer = self._peer
+        marks = []
+
+        def mark(name):
+            if self.time_phases:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        if topk is None:
+            ids, w = self.backend.route(x)
+            ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
+        else:
+            ids, w = topk
+        mark("route")
+        # this rank's tokens and a zeroed output, where every rank can reach them
+        x_sym, out_sym = peer["x"][:T], peer["out"][:T]
+        x_sym.copy_(x)
+        out_sym.zero_()
+        # routing records straight into the destination ranks' receive areas, then the counts
+        cap = peer["max_tokens"]
+        cursor = peer["cursor"]
+        cursor.zero_()
+        self.backend.pack_meta_peer(ids, w, self.n_shared, world, rank, self.begins, cursor, peer["meta_bases"],
+                                    peer["cnt_bases"], cap)
+        mark("records")
+        # every rank's tokens, records and counts are in place and its output rows are zero
+        peer["hx"].barrier(channel=0)
+        mark("barrier_in")
+        r_ids, r_w, a_rows, out_rows = peer["ids"], peer["w"], peer["a_rows"], peer["out_rows"]
+        self.backend.unpack_meta_peer(peer["meta"], peer["cnt"], world, cap, slots, peer["x_bases"],
+                                      peer["out_bases"], H, r_ids, r_w, a_rows, out_rows)
+        self.backend.experts_rows(a_rows, out_rows, r_ids, r_w)
+        mark("experts")
+        R_send = R_recv = local_slots = None
+        if self.count_local_slots:   # host reads, for reporting only
+            R_send, R_recv = int(cursor.sum()), int(peer["cnt"][:world].sum())
+            local_slots = int((r_ids >= 0).sum())
+        # every rank's additions into this rank's output rows are done
+        peer["ho"].barrier(channel=0)
+        mark("barrier_out")
+        out = torch.empty((T, H), dtype=x.dtype, device=dev)
+        out.copy_(out_sym)
+        mark("convert")
+        phase_ms = None
+        if self.time_phases:
+            torch.cuda.synchronize(dev)
+            phase_ms = {marks[i + 1][0]: round(marks[i][1].elapsed_time(marks[i + 1][1]), 4) for i in range(len(marks) - 1)}
+        stride = 1 + 2 * slots
+        known = R_recv is not None
+        self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T, "form": "peer memory",
+                       "launches_per_step": 2 + 3 + 1 + (1 if world * cap * slots <= 1024 else 3) + 4,
+                       "dispatch_bytes": R_send * stride * 4 if known else None, "combine_bytes": 0,
+                       "peer_read_bytes": R_recv * H * 2 if known else None,
+                       "peer_add_bytes": R_recv * H * 4 if known else None,
+                       "local_slots": local_slots, "phase_ms": phase_ms}
+        return out
+
     def forward(self, x: torch.Tensor, topk=None) -> torch.Tensor:
         """x [T_local, H] bf16 -> bf16 [T_local, H]. `topk` = (ids [T, k] int32 GLOBAL expert ids,
         weights [T, k] fp32) skips the router."""
+        if self._peer is not None and x.shape[0] <= self._peer["max_tokens"]:
+            return self._forward_peer(x, topk)
         T, H = x.shape
         world, rank, slots = self.world, self.rank, self.slots
         dev = x.device
@@ -192,7 +346,7 @@ class ExpertParallelMoE:
         self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T,
                        "launches_per_step": 2 + 2 + 1 + (1 if R_recv * slots <= 1024 else 3) + 4,
                        "dispatch_bytes": R_send * (H * 2 + slots * 8), "combine_bytes": R_recv * H * 4,
-                       "local_slots": local_slots, "phase_ms": phase_ms}
+                       "form": "collective", "local_slots": local_slots, "phase_ms": phase_ms}
         return out
 
     __call__ = forward

@@ -182,6 +182,22 @@ class FusedMoEMxfp4:
         y.copy_(out)
         return y
 
+    def experts_rows(self, a_rows, out_rows, topk_ids, topk_w):
+        """Alignment + the two grouped GEMMs on rows given by ADDRESS (int64 [R] each): reads
+        every activation row where it lives and adds every result row where it belongs (see
+        ``ops.fused_moe_mxfp4_rows_into``). The output rows must be zeroed by their owner."""
+        R = a_rows.shape[0]
+        bufs = self._buffers(R)
+        em = self._em_bound(R)
+        sids, eids, _ = ops.moe_align_block_size(
+            topk_ids, self.n_experts_total, self.block_size, max_EM=em,
+            out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
+        ops.fused_moe_mxfp4_rows_into(bufs["act"], a_rows, out_rows, self.w13, self.w13_scale, self.w2,
+                                      self.w2_scale, topk_w.reshape(-1), sids, eids,
+                                      top_k=topk_ids.shape[1], block_size=self.block_size,
+                                      swiglu_limit=self.swiglu_limit, activation=self.activation,
+                                      beta=self.beta, linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+
     def forward(self, x: torch.Tensor, *, logits: torch.Tensor | None = None, out_bf16=None):
         """route -> align -> gate/up -> down+combine, all on the current stream."""
         ops.require(x.dim() == 2 and x.shape[1] == self.hidden, "x must be [T, hidden]")
