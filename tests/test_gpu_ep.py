@@ -40,7 +40,7 @@ def _worker(rank, world, port, tmp):
         from vkernels_b200.dist import ExpertParallelMoE
         from vkernels_b200.experts import layer_from_config
 
-        cfg = syn.scaled(syn.CONFIGS["c0"], E=6, top_k=3)   # 6 experts over 2 ranks, uneven use
+        cfg = syn.scaled(syn.CONFIGS["c0"], E=max(6, world + 1), top_k=3)   # uneven split of the experts
         T_local = 48
         T = T_local * world
         ep = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T_local)
@@ -90,10 +90,11 @@ def _worker(rank, world, port, tmp):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_ranks_match_single_rank(tmp_path, oracle_mod):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_ranks_match_single_rank(world, tmp_path, oracle_mod):
     import torch.multiprocessing as mp
-    world = 2
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         txt = (tmp_path / f"rank{r}.txt").read_text()
