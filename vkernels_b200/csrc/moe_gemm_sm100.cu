@@ -79,6 +79,9 @@ constexpr int kTmemCols = 512;
 constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
 constexpr int kEpiStageBytes = 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds)
 constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
+// Lone-CTA form: byte -> bf16 pair lookup table in shared memory, one copy per bank (lane l reads
+// word 32 * byte + l), so a warp's 32 lookups of different bytes are one conflict-free access.
+constexpr int kLutBytes = 256 * 32 * 4;
 constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of SM clock
 
 struct TokTile {
@@ -150,13 +153,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait. Returns false when the CTA is aborting (this wait or another
 // role's ran out of iterations).
+// `sleep_ns` > 0 is for waits that are long and off the critical path (an epilogue warp waiting
+// for a whole item's MMAs, a producer waiting for a free slot of a deep ring): the warp sleeps
+// between polls instead of spending issue slots that the dequant warps of the same scheduler need.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
+                                          int code, unsigned sleep_ns = 0) {
   // try_wait suspends the thread for a hardware-chosen slice, so the limit is kept in clock
   // cycles rather than in poll iterations.
   long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if ((it & 63u) == 63u) {
       if (*abort_flag) return false;
       const long long now = clock64();
@@ -385,6 +392,50 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
+// Eight nibbles of `w` times one scale through the shared-memory table (see kLutBytes): per byte
+// one integer-pipe instruction to isolate it, one multiply-add for the address, one load, one
+// bf16x2 multiply - a quarter of the integer-pipe work of the permute-based dequant8, which is
+// what bounds a decode-size batch. Same bits: table value (exact) times scale in one bf16 multiply.
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void dequant8_lut(uint32_t w, uint32_t scale2, uint32_t lut_lane, uint32_t out[4]) {
+  const uint32_t b0 = w & 0xFFu, b1 = prmt(w, 0u, 0x4441u), b2 = prmt(w, 0u, 0x4442u), b3 = w >> 24;
+  out[0] = mul_bf16x2(lds_u32(lut_lane + b0 * 128u), scale2);
+  out[1] = mul_bf16x2(lds_u32(lut_lane + b1 * 128u), scale2);
+  out[2] = mul_bf16x2(lds_u32(lut_lane + b2 * 128u), scale2);
+  out[3] = mul_bf16x2(lds_u32(lut_lane + b3 * 128u), scale2);
+}
+// 64 nibbles (two 16-byte chunks, one scale each) in three passes over the same 32 registers:
+// all table addresses, all loads, all multiplies - every pass is 32 independent instructions,
+// so a lone warp keeps its pipes busy instead of walking one dependent chain at a time.
+__device__ __forceinline__ void dequant64_lut(const uint4& p0, const uint4& p1, uint32_t s0, uint32_t s1,
+                                              uint32_t lut_lane, uint32_t (&v)[32]) {
+  const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[4 * i + 0] = lut_lane + (w[i] & 0xFFu) * 128u;
+    v[4 * i + 1] = lut_lane + prmt(w[i], 0u, 0x4441u) * 128u;
+    v[4 * i + 2] = lut_lane + prmt(w[i], 0u, 0x4442u) * 128u;
+    v[4 * i + 3] = lut_lane + (w[i] >> 24) * 128u;
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = lds_u32(v[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = mul_bf16x2(v[i], s0);
+#pragma unroll
+  for (int i = 16; i < 32; ++i) v[i] = mul_bf16x2(v[i], s1);
+}
+// bf16 bit pattern of one nibble code (sign in bit 3) under the layer's table
+__device__ __forceinline__ uint32_t e2m1_bf16_bits(uint32_t code) {
+  const uint32_t m = code & 7u;
+  const uint32_t mag = m == 0 ? 0x0000u : m == 1 ? 0x3E80u : m == 2 ? 0x3F80u : m == 3 ? 0x3FC0u
+                     : m == 4 ? 0x4000u : m == 5 ? 0x4040u : m == 6 ? 0x7F80u : 0x7FC0u;
+  return mag | ((code & 8u) << 12);
+}
+
 __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
@@ -464,10 +515,19 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
   // gate/up epilogue staging: 2 x (32 tokens x 64 features) bf16, 16-byte aligned
   uint16_t* epi_stage = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(Barriers) + 127) & ~size_t(127)));
+  constexpr bool kUseLut = CTAS == 1;
+  uint32_t* lut = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(epi_stage) +
+                                              (GATEUP ? kEpiStageBytes : kEpiStageDownBytes));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
+  if (kUseLut) {
+    for (int i = tid; i < 256 * 32; i += kThreads) {
+      const uint32_t byte = (uint32_t)i >> 5;
+      lut[i] = e2m1_bf16_bits(byte & 15u) | (e2m1_bf16_bits(byte >> 4) << 16);
+    }
+  }
   if (tid == 0) {
     for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
@@ -548,7 +608,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         {
           const int sb = sc_it % p.scale_bufs;
           const uint32_t par = ((sc_it / p.scale_bufs) & 1u) ^ 1u;
-          if (!mbar_wait(smem_u32(&bars->sc_empty[sb]), par, abort_flag, 1)) break;
+          if (!mbar_wait(smem_u32(&bars->sc_empty[sb]), par, abort_flag, 1, 128)) break;
           const uint32_t bar = smem_u32(&bars->sc_full[sb]);
           const uint32_t dst = smem_u32(sc_smem + sb * p.scale_buf_bytes);
           const uint32_t half = 64u * pitch;
@@ -563,7 +623,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           ++sc_it;
         }
         for (int kw = 0; kw < n_kw; ++kw) {
-          if (!mbar_wait(smem_u32(&bars->w_empty[w.slot]), w.phase ^ 1u, abort_flag, 2)) {
+          if (!mbar_wait(smem_u32(&bars->w_empty[w.slot]), w.phase ^ 1u, abort_flag, 2, 128)) {
             ok = false;
             break;
           }
@@ -601,7 +661,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const int row_main = tt.row0 + (int)cta_rank * h0;
           const int row_ext = tt.row0 + 2 * h0 + (int)cta_rank * h1;
           for (int st = 0; st < n_stages; ++st) {
-            if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 3)) {
+            if (!mbar_wait(smem_u32(&bars->stage_done[a.slot]), a.phase ^ 1u, abort_flag, 3, 64)) {
               ok = false;
               break;
             }
@@ -629,7 +689,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const TokTile tt = p.tiles[item / n_fgroups];
         for (int st = 0; st < n_stages; ++st, ++issued) {
           if (issued >= p.b_stages) {
-            if (!mbar_wait(smem_u32(&bars->stage_done[lag.slot]), lag.phase, abort_flag, 3)) {
+            if (!mbar_wait(smem_u32(&bars->stage_done[lag.slot]), lag.phase, abort_flag, 3, 64)) {
               ok = false;
               break;
             }
@@ -770,6 +830,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // the accumulator hands one thread the gate and the up value of the same (feature, token).
     const int srow = GATEUP ? (((row >> 3) & 1) * 64 + (row >> 4) * 8 + (row & 7)) : row;   // row inside the staged tile
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols;
+    const uint32_t lut_lane = smem_u32(lut) + (uint32_t)lane * 4u;
     Ring w, a;
     uint32_t sc_it = 0;
     int turn = 0;   // which dequant set takes the coming stage, running over all items
@@ -823,14 +884,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const uint4 p1 = *reinterpret_cast<const uint4*>(my_row + (((c0 + 1) ^ (srow & 7)) << 4));
                 const uint32_t s0 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0]);
                 const uint32_t s1 = ue8m0_to_bf16x2(my_scales[kw * 8 + c0 + 1]);
-                dequant8(p0.x, s0, v + 0);
-                dequant8(p0.y, s0, v + 4);
-                dequant8(p0.z, s0, v + 8);
-                dequant8(p0.w, s0, v + 12);
-                dequant8(p1.x, s1, v + 16);
-                dequant8(p1.y, s1, v + 20);
-                dequant8(p1.z, s1, v + 24);
-                dequant8(p1.w, s1, v + 28);
+                if (kUseLut) {
+                  dequant64_lut(p0, p1, s0, s1, lut_lane, v);
+                } else {
+                  dequant8(p0.x, s0, v + 0);
+                  dequant8(p0.y, s0, v + 4);
+                  dequant8(p0.z, s0, v + 8);
+                  dequant8(p0.w, s0, v + 12);
+                  dequant8(p1.x, s1, v + 16);
+                  dequant8(p1.y, s1, v + 20);
+                  dequant8(p1.z, s1, v + 24);
+                  dequant8(p1.w, s1, v + 28);
+                }
               } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = 0u;
@@ -875,7 +940,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
       named_bar_sync(1, 128);
-      if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10)) break;
+      if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256)) break;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       auto release_acc = [&]() {
@@ -1214,7 +1279,8 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
-  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : kEpiStageDownBytes) + 128;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : kEpiStageDownBytes) + 128 +
+                    (CTAS == 1 ? kLutBytes : 0);
   // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
   p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
   // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot

@@ -207,6 +207,24 @@ class FusedMoEMxfp4:
 
     __call__ = forward
 
+    def capture(self, x: torch.Tensor):
+        """Captures ``forward(x)`` into a CUDA graph. Returns ``(graph, y)``: ``graph.replay()`` reruns the
+        whole step (router, alignment, both GEMMs, conversion) on whatever ``x``'s storage holds
+        then and leaves the result in ``y``. A decode step is a dozen short kernels; replaying
+        them as one graph removes the launch gaps between them. Everything the step needs is
+        allocated before the capture (two eager warm-up calls)."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.forward(x)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y = self.forward(x)
+        return graph, y
+
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
         """Host activations in, host bf16 result out (both pinned), copies included; returns after
         the result has landed."""
