@@ -212,6 +212,24 @@ def test_token_tile_edges_of_the_cta_pair_form(n_hot):
     assert_close_bf16(got, ref, f"{n_hot} tokens on one expert")
 
 
+def test_status_word_survives_the_alignment_scratch():
+    """The chunked alignment (more than 1024 routed slots) keeps its histograms in the library
+    workspace, whose first 4 KB also hold the GEMM kernels' status word. With 16 local experts
+    the second chunk's first counter used to land exactly on that word and made a healthy run
+    look like a timed-out one."""
+    cfg = syn.scaled(syn.CONFIGS["c0"], H=512, I=256, E=16, top_k=4)
+    T = 1536
+    w, A, _ = make_case(cfg, T)
+    rng = np.random.default_rng(16)
+    ids = np.stack([rng.permutation(cfg.E)[: cfg.top_k] for _ in range(T)]).astype(np.int32)
+    tw = rng.random((T, cfg.top_k), dtype=np.float32)
+    tokens = np.sort(rng.choice(T, 48, replace=False))
+    idt, twt = torch.from_numpy(ids).to(DEV), torch.from_numpy(tw).to(DEV)
+    got = to_np(gpu_layer(A, w, idt, twt, impl="tcgen05"))   # gpu_layer checks the status word
+    ref = oracle_layer(A, w, idt, twt, tokens=tokens)
+    assert_close_bf16(got[tokens], ref, "16 experts, 6144 routed slots")
+
+
 def test_c3_shape_with_shared_expert_on_a_token_subsample():
     cfg = syn.CONFIGS["c3"]
     T = 4096   # the full T = 16384 runs in bench.py; the weights (5.7 GB) are full size here

@@ -215,7 +215,10 @@ void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, in
                                                local_n, max_EM, sorted_ids, expert_ids, out_em);
   } else {
     const int n_chunks = (N + kChunk - 1) / kChunk;
-    int* ws = static_cast<int*>(workspace_get(((size_t)n_chunks * ln + ln) * sizeof(int)));
+    // The first 4 KB of the workspace hold the tile count and the status word of the GEMM
+    // kernels, which must survive from call to call: the histograms start behind them.
+    int* ws = reinterpret_cast<int*>(
+        static_cast<uint8_t*>(workspace_get(4096 + ((size_t)n_chunks * ln + ln) * sizeof(int))) + 4096);
     int* hist = ws;
     int* offset = ws + (size_t)n_chunks * ln;
     if (hist_smem > 48 * 1024) {
