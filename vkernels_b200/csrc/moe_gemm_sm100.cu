@@ -46,6 +46,7 @@
 // (moe_fused.hip:1448-1663).
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -1435,6 +1436,16 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // A token meets an expert at most once, so no expert holds more than M rows (+ padding).
   int max_tok = ((M + block_size - 1) / block_size) * block_size;
   max_tok = ((max_tok + 15) / 16) * 16;
+  // When an expert sees a few dozen tokens at most, tiles are capped at 64 rows so that the launch
+  // takes the long-stage form built for small tiles (an expert with more rows is split into
+  // several items); measured crossover against the CTA-pair form: about 48 tokens per expert.
+  // The expert count is not an argument of the layer: callers size EM as N + E * (block - 1),
+  // which gives a lower bound of E (an exact EM only makes the estimate more conservative).
+  {
+    const long long n_slots = (long long)M * top_k;
+    const long long e_est = std::max<long long>(1, ((long long)EM - n_slots) / (block_size - 1));
+    if ((M <= 256 || n_slots <= 48 * e_est) && max_tok > 64) max_tok = 64;
+  }
   // Tiles over 128 tokens go to CTA pairs when both GEMMs fit shared memory in that form.
   bool use_pair = false;
   if (max_tok > 128 && pair_mode()) {
