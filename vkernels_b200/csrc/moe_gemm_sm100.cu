@@ -393,21 +393,14 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
-// Eight nibbles of `w` times one scale through the shared-memory table (see kLutBytes): per byte
-// one integer-pipe instruction to isolate it, one multiply-add for the address, one load, one
-// bf16x2 multiply - a quarter of the integer-pipe work of the permute-based dequant8, which is
-// what bounds a decode-size batch. Same bits: table value (exact) times scale in one bf16 multiply.
+// Expansion through the shared-memory table (see kLutBytes): per byte of packed weights one
+// integer-pipe instruction to isolate it, one multiply-add for the address, one load and one
+// bf16x2 multiply - a quarter of the integer-pipe work of the permute-based dequant8. Same
+// bits: table value (exact) times scale in one bf16 multiply.
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
-}
-__device__ __forceinline__ void dequant8_lut(uint32_t w, uint32_t scale2, uint32_t lut_lane, uint32_t out[4]) {
-  const uint32_t b0 = w & 0xFFu, b1 = prmt(w, 0u, 0x4441u), b2 = prmt(w, 0u, 0x4442u), b3 = w >> 24;
-  out[0] = mul_bf16x2(lds_u32(lut_lane + b0 * 128u), scale2);
-  out[1] = mul_bf16x2(lds_u32(lut_lane + b1 * 128u), scale2);
-  out[2] = mul_bf16x2(lds_u32(lut_lane + b2 * 128u), scale2);
-  out[3] = mul_bf16x2(lds_u32(lut_lane + b3 * 128u), scale2);
 }
 // 64 nibbles (two 16-byte chunks, one scale each) in three passes over the same 32 registers:
 // all table addresses, all loads, all multiplies - every pass is 32 independent instructions,
