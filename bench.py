@@ -56,8 +56,46 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.stop = threading.Event()
+        self.t = None
+
+    # NVML (read-only queries) every 5 ms when the module is there, else nvidia-smi every 100 ms:
+    # the timed region of a default run is a few tens of milliseconds long.
+    def _poll_nvml(self, nv, h):
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        sm_max = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                mask = int(get_reasons(h))
+                row = [str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(sm_max),
+                       str(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)]
+                row += ["Active" if mask & bit else "Not Active" for bit in names.values()]
+                self.rows.append(row)
+            except Exception:  # noqa: BLE001 - a failed sample is skipped
+                pass
+            self.stop.wait(0.005)
 
     def __enter__(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            uuid = None
+            try:
+                uuid = torch.cuda.get_device_properties(self.index).uuid
+            except Exception:  # noqa: BLE001
+                pass
+            h = nv.nvmlDeviceGetHandleByUUID(f"GPU-{uuid}") if uuid is not None else nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.t = threading.Thread(target=self._poll_nvml, args=(nv, h), daemon=True)
+            self.t.start()
+            return self
+        except Exception:  # noqa: BLE001 - fall back to the command-line tool
+            self.t = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
@@ -75,12 +113,15 @@ class ClockSampler:
                 self.rows.append(parts)
 
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        elif self.t is not None:
+            self.t.join(timeout=1)
 
     def summary(self):
         if not self.rows:
