@@ -174,11 +174,16 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) total[n][j] = 0.0f;
 
-  const int n_chunks = (H + MK - 1) / MK;
-  load_chunk(0);
-  store_chunk(0);
+  // gridDim.z == 2 splits the reduction in two halves that are added into zeroed logits with
+  // atomics: a sum of two partials does not depend on their order, so the result stays
+  // reproducible, and a batch too small to fill the machine gets twice the CTAs.
+  const int all_chunks = (H + MK - 1) / MK;
+  const int ch_begin = (int)blockIdx.z * all_chunks / (int)gridDim.z;
+  const int n_chunks = ((int)blockIdx.z + 1) * all_chunks / (int)gridDim.z;
+  load_chunk(ch_begin * MK);
+  store_chunk(ch_begin & 1);
   __syncthreads();
-  for (int ch = 0; ch < n_chunks; ++ch) {
+  for (int ch = ch_begin; ch < n_chunks; ++ch) {
     const int buf = ch & 1;
     if (ch + 1 < n_chunks) load_chunk((ch + 1) * MK);
     float part[NT][4];
@@ -221,8 +226,13 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
     for (int half = 0; half < 2; ++half) {
       const int t = r0 + half * 8;
       if (t >= T) continue;
-      if (e < E) logits[(size_t)t * E + e] = total[n][half * 2];
-      if (e + 1 < E) logits[(size_t)t * E + e + 1] = total[n][half * 2 + 1];
+      if (gridDim.z == 1) {
+        if (e < E) logits[(size_t)t * E + e] = total[n][half * 2];
+        if (e + 1 < E) logits[(size_t)t * E + e + 1] = total[n][half * 2 + 1];
+      } else {
+        if (e < E) atomicAdd(logits + (size_t)t * E + e, total[n][half * 2]);
+        if (e + 1 < E) atomicAdd(logits + (size_t)t * E + e + 1, total[n][half * 2 + 1]);
+      }
     }
   }
 }
@@ -437,6 +447,10 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
           x, wr, logits, T, H, E);
     } else {
       dim3 grid(t_tiles, (E + 63) / 64);
+      if ((int)(grid.x * grid.y) < 148 && H >= 4 * MK) {   // not enough CTAs for the machine: split K in two
+        grid.z = 2;
+        VK_CUDA_CHECK(cudaMemsetAsync(logits, 0, (size_t)T * E * sizeof(float), static_cast<cudaStream_t>(stream)));
+      }
       router_logits_mma_kernel<64><<<grid, 256, sizeof(RouterSmem<64>), static_cast<cudaStream_t>(stream)>>>(
           x, wr, logits, T, H, E);
     }
