@@ -47,6 +47,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -1297,11 +1298,14 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   p.scale_bufs = scale_bufs;
   p.scale_buf_bytes = scale_tile;
   const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWStageBytes;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the device's context: once per device and instantiation
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev].load()) {
     VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true);
   }
   if (CTAS == 1) {
     moe_gemm_sm100_kernel<GATEUP, KS, CTAS><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);

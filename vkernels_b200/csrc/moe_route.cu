@@ -10,6 +10,7 @@
 // rule used is the DeepSeek-V3 one: a group's score is the sum of its two
 // largest biased scores and only experts of the topk_group best groups stay
 // eligible.
+#include <atomic>
 #include "common.cuh"
 #include "moe_fused.hpp"
 
@@ -432,13 +433,17 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
         x, wr, logits, T, H, E);
   } else if (H % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
              (reinterpret_cast<uintptr_t>(wr) & 15u) == 0) {
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the device's context: once per device
+    static std::atomic<bool> configured_dev[64];
+    int dev = 0;
+    VK_CUDA_CHECK(cudaGetDevice(&dev));
+    const bool known = dev >= 0 && dev < 64;
+    if (!known || !configured_dev[dev].load()) {
       VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)sizeof(RouterSmem<128>)));
       VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)sizeof(RouterSmem<64>)));
-      configured = true;
+      if (known) configured_dev[dev].store(true);
     }
     const int t_tiles = (T + MT - 1) / MT;
     if (t_tiles * ((E + 127) / 128) >= 2 * 148) {
