@@ -22,8 +22,10 @@
 //               256-K stage) and scale bytes (bulk copy per item)
 //   warp 1      tcgen05.mma issuer + tensor-memory allocation
 //   warp 2      TMA producer: token tiles
-//   warps 4-15  dequant: shared memory -> registers -> tensor memory (three sets of four)
-//   warps 16-19 epilogue: tensor memory -> registers -> global
+//   warps 4-11  dequant: shared memory -> registers -> tensor memory (two sets of four, a
+//               stage each in turn)
+//   warps 12-19 epilogue: tensor memory -> registers -> global (two sets of four; the 32-token
+//               rounds of the gate/up epilogue alternate between them)
 //
 // Two forms, chosen by the largest token tile of the launch:
 //   lone CTA (tiles up to 128 tokens, the decode regime): the stage length grows as the tile
@@ -74,12 +76,13 @@ constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per laun
 constexpr int kMaxAStages = 8;
 constexpr int kMaxBStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
-constexpr int kDequantSets = 3;      // dequant warps per tensor-memory lane quarter
+constexpr int kDequantSets = 2;      // dequant warps per tensor-memory lane quarter
+constexpr int kEpiSets = 2;          // epilogue warps per lane quarter (they take the 32-token rounds in turn)
 constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
-constexpr int kThreads = (kEpiWarp0 + 4) * 32;
+constexpr int kThreads = (kEpiWarp0 + 4 * kEpiSets) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
-constexpr int kEpiStageBytes = 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds)
+constexpr int kEpiStageBytes = kEpiSets * 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds per set)
 constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
 // Lone-CTA form: byte -> bf16 pair lookup table in shared memory, one copy per bank (lane l reads
 // word 32 * byte + l), so a warp's 32 lookups of different bytes are one conflict-free access.
@@ -538,7 +541,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->sc_empty[i]), 4 * kDequantSets);
     }
     mbar_init(smem_u32(&bars->acc_full), 1);
-    mbar_init(smem_u32(&bars->acc_empty), 4 * CTAS);
+    mbar_init(smem_u32(&bars->acc_empty), 4 * kEpiSets * CTAS);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -913,16 +916,21 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     retire();
   } else if (warp >= kEpiWarp0) {
     // ------------------------------ epilogue -------------------------------
+    // Two sets of four warps (one per lane quarter): the gate/up rounds of 32 tokens alternate
+    // between them, which halves the time the MMA issuer waits for the accumulator; the down
+    // epilogue runs on the first set only (its staging area is a block per warp).
     const int q = warp & 3;
-    const int etid = tid - kEpiWarp0 * 32;  // 0..127 = TMEM lane
+    const int es = (warp - kEpiWarp0) >> 2;          // epilogue set
+    const int etid = tid - kEpiWarp0 * 32;           // 0 .. 128 * kEpiSets - 1
+    const int ltid = etid & 127;                     // thread inside the set = TMEM lane
     uint32_t acc_phase = 0;
-    int round = 0;   // gate/up staging buffer parity, running over all items
+    int round = 0;   // gate/up staging buffer parity of this set, running over all items
     for (int item = unit; item < n_items; item += n_units, acc_phase ^= 1u) {
       const TokTile tt = p.tiles[item / n_fgroups];
       const int f = item_f(item);
       // per-token info of this item (previous item's readers are past the barrier below)
-      named_bar_sync(1, 128);
-      for (int j = etid; j < tt.n_rows; j += 128) {
+      named_bar_sync(1, 128 * kEpiSets);
+      for (int j = etid; j < tt.n_rows; j += 128 * kEpiSets) {
         const int flat = p.sorted_ids[tt.row0 + j];
         const bool real = flat >= 0 && flat < p.N;
         if (GATEUP) {
@@ -934,7 +942,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
-      named_bar_sync(1, 128);
+      named_bar_sync(1, 128 * kEpiSets);
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256)) break;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -946,8 +954,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           else mbar_arrive(smem_u32(&bars->acc_empty));
         }
       };
-      if (f >= p.n_ftiles) {   // idle half of the last pair
-        release_acc();
+      if (f >= p.n_ftiles || (!GATEUP && es != 0) || (GATEUP && es * 32 >= tt.n_rows)) {
+        release_acc();   // idle half of the last pair, or a set with no round in this item
         continue;
       }
       if (GATEUP) {
@@ -962,18 +970,19 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const float* bp = p.bias + (size_t)tt.expert * 2 * p.n_feat + f * 64 + fl;
           bg[0] = bp[0]; bg[1] = bp[8]; bu[0] = bp[p.n_feat]; bu[1] = bp[p.n_feat + 8];
         }
-        for (int c0 = 0; c0 < tt.n_rows; c0 += 32, ++round) {
+        uint16_t* const my_stage = epi_stage + es * (2 * 32 * kEpiPitch);
+        for (int c0 = es * 32; c0 < tt.n_rows; c0 += 32 * kEpiSets, ++round) {
           uint32_t va[16], vb[16];
           tc_ld_16x256b_x4(t_lane + c0, va);
           tc_ld_16x256b_x4(t_lane + (16u << 16) + c0, vb);
           tc_wait_ld();
-          if (c0 + 32 >= tt.n_rows) release_acc();   // last read of the accumulator
+          if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
           // which of the round's 32 tokens are real rows: one shared-memory read per lane and
           // a ballot, so the stores below depend on no load
           const int my_t = c0 + lane;
           const unsigned real = __ballot_sync(0xFFFFFFFFu, my_t < tt.n_rows && bars->tile_ref[my_t] != 0ull);
           // activation -> bf16 into the staging tile [token][feature] of this round ...
-          uint16_t* stg = epi_stage + (round & 1) * (32 * kEpiPitch) + tk * kEpiPitch + fl;
+          uint16_t* stg = my_stage + (round & 1) * (32 * kEpiPitch) + tk * kEpiPitch + fl;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -993,13 +1002,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           // ... then rows leave as 16-byte pieces: 8 consecutive threads write one 128-byte act row.
           // One barrier per round: a buffer is rewritten two rounds later, after the barrier of
           // the round in between, which every reader of this round has passed by then.
-          named_bar_sync(2, 128);
+          named_bar_sync(2 + es, 128);
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const int piece = etid + i * 128;           // 256 pieces of 16 bytes
+            const int piece = ltid + i * 128;           // 256 pieces of 16 bytes
             const int tok = piece >> 3, ch = piece & 7;
             if ((real >> tok) & 1u) {
-              const uint4 val = *reinterpret_cast<const uint4*>(epi_stage + (round & 1) * (32 * kEpiPitch) + tok * kEpiPitch + ch * 8);
+              const uint4 val = *reinterpret_cast<const uint4*>(my_stage + (round & 1) * (32 * kEpiPitch) + tok * kEpiPitch + ch * 8);
               *reinterpret_cast<uint4*>(p.act + (size_t)(tt.row0 + c0 + tok) * p.n_feat + f * 64 + ch * 8) = val;
             }
           }
