@@ -917,8 +917,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   } else if (warp >= kEpiWarp0) {
     // ------------------------------ epilogue -------------------------------
     // Two sets of four warps (one per lane quarter): the gate/up rounds of 32 tokens alternate
-    // between them, which halves the time the MMA issuer waits for the accumulator; the down
-    // epilogue runs on the first set only (its staging area is a block per warp).
+    // between them, and so do the rounds of the down epilogue, which halves the time the MMA
+    // issuer waits for the accumulator.
     const int q = warp & 3;
     const int es = (warp - kEpiWarp0) >> 2;          // epilogue set
     const int etid = tid - kEpiWarp0 * 32;           // 0 .. 128 * kEpiSets - 1
@@ -954,7 +954,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           else mbar_arrive(smem_u32(&bars->acc_empty));
         }
       };
-      if (f >= p.n_ftiles || (!GATEUP && es != 0) || (GATEUP && es * 32 >= tt.n_rows)) {
+      if (f >= p.n_ftiles || es * 32 >= tt.n_rows || (!GATEUP && (p.n_feat & 3) != 0 && es != 0)) {
         release_acc();   // idle half of the last pair, or a set with no round in this item
         continue;
       }
@@ -1020,31 +1020,36 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           // shared memory, so a lane holds four consecutive output features of one token and
           // adds them with one red.v4 (a quarter of the reduction instructions, which are what
           // this epilogue is bound by). Lane l: features 4 * (l % 8).., tokens l / 8 + 4 * i.
-          float* stage = reinterpret_cast<float*>(epi_stage) + q * (32 * 32);
+          // The two warp sets take the 32-token rounds in turn; a warp's block is 16 tokens wide,
+          // so a round goes through it in two halves.
+          float* stage = reinterpret_cast<float*>(epi_stage) + (es * 4 + q) * (16 * 32);
           const int hq = (lane & 7) * 4;                 // feature quad inside the warp's 32 rows
           const int h0 = f * 128 + q * 32 + hq;
           const bool quad_ok = q * 32 + hq < rows_valid;
           float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
           if (p.bias && quad_ok) b4 = *reinterpret_cast<const float4*>(p.bias + (size_t)tt.expert * p.n_feat + h0);
-          for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
+          for (int c0 = es * 32; c0 < tt.n_rows; c0 += 32 * kEpiSets) {
             uint32_t v[32];
             tc_ld32(t_lane + c0, v);
             tc_wait_ld();
-            if (c0 + 32 >= tt.n_rows) release_acc();
-            __syncwarp();   // the previous block has been read
+            if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
 #pragma unroll
-            for (int j = 0; j < 32; ++j) stage[j * 32 + lane] = __uint_as_float(v[j]);
-            __syncwarp();
+            for (int half = 0; half < 2; ++half) {
+              __syncwarp();   // the previous block has been read
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int tl = (lane >> 3) + 4 * i;
-              const int t = c0 + tl;
-              float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
-              if (orow != nullptr && quad_ok) {
-                const float wgt = bars->tile_w[t];
-                const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
-                red_add_v4(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
-                           (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
+              for (int j = 0; j < 16; ++j) stage[j * 32 + lane] = __uint_as_float(v[half * 16 + j]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int tl = (lane >> 3) + 4 * i;
+                const int t = c0 + half * 16 + tl;
+                float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
+                if (orow != nullptr && quad_ok) {
+                  const float wgt = bars->tile_w[t];
+                  const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                  red_add_v4(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
+                             (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
+                }
               }
             }
           }
