@@ -22,10 +22,10 @@
 //               256-K stage) and scale bytes (bulk copy per item)
 //   warp 1      tcgen05.mma issuer + tensor-memory allocation
 //   warp 2      TMA producer: token tiles
-//   warps 4-11  dequant: shared memory -> registers -> tensor memory (two sets of four, a
-//               stage each in turn)
-//   warps 12-19 epilogue: tensor memory -> registers -> global (two sets of four; the 32-token
-//               rounds of the gate/up epilogue alternate between them)
+//   warps 4-19  sixteen workers in sets of four (one warp per tensor-memory lane quarter):
+//               dequant sets (shared memory -> registers -> tensor memory, a stage each in
+//               turn) and epilogue sets (tensor memory -> registers -> global, a 32-token round
+//               each in turn) - two + two for a CTA pair, three + one for a lone CTA
 //
 // Two forms, chosen by the largest token tile of the launch:
 //   lone CTA (tiles up to 128 tokens, the decode regime): the stage length grows as the tile
@@ -76,13 +76,16 @@ constexpr int kMaxWStages = 8;    // packed-weight ring depth is chosen per laun
 constexpr int kMaxAStages = 8;
 constexpr int kMaxBStages = 8;
 constexpr int kWStageBytes = kRows * 128;          // 16 KB
-constexpr int kDequantSets = 2;      // dequant warps per tensor-memory lane quarter
-constexpr int kEpiSets = 2;          // epilogue warps per lane quarter (they take the 32-token rounds in turn)
-constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
-constexpr int kThreads = (kEpiWarp0 + 4 * kEpiSets) * 32;
+// 16 worker warps after the four control warps, split by form: a CTA pair (prefill) runs two
+// dequant sets and two epilogue sets (the accumulator drains twice as fast, which is what its
+// MMA issuer waits for); a lone CTA (decode) runs three dequant sets and one epilogue set (its
+// epilogue is a few rounds, its bound is the expansion).
+constexpr int dequant_sets(int ctas) { return ctas == 2 ? 2 : 3; }   // dequant warps per TMEM lane quarter
+constexpr int epi_sets(int ctas) { return ctas == 2 ? 2 : 1; }       // epilogue warps per lane quarter
+constexpr int kThreads = (4 + 4 * 4) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
-constexpr int kEpiStageBytes = kEpiSets * 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds per set)
+constexpr int kEpiStageBytes = 2 * 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds per set, up to two sets)
 constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
 // Lone-CTA form: byte -> bf16 pair lookup table in shared memory, one copy per bank (lane l reads
 // word 32 * byte + l), so a warp's 32 lookups of different bytes are one conflict-free access.
@@ -501,6 +504,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // expected on the same barrier the dequant warps arrive on, so the MMA issuer polls a single
   // barrier per stage.
   constexpr bool kMerged = CTAS == 2;
+  constexpr int kDequantSets = dequant_sets(CTAS), kEpiSets = epi_sets(CTAS);
+  constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
+  static_assert((kEpiWarp0 + 4 * kEpiSets) * 32 == kThreads, "the role split must use every warp");
   const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
 
