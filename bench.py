@@ -7,8 +7,9 @@ One step = one pass of the hot path (route -> align -> gate/up GEMM + activation
 fused weighted combine) over one batch of seeded synthetic tokens. Default workload: the
 gpt-oss-120b-shaped prefill layer (H = I = 2880, E = 128, top-4, T = 8192), the configuration the
 headline metric is quoted on at 1, 2, 4 and 8 GPUs; with --gpus N > 1 (launched under torchrun)
-the experts are partitioned over the ranks and tokens travel by NCCL all-to-all (strong scaling:
-the global batch is fixed). The same JSON line also carries the single-GPU decode sweep of the
+the experts are partitioned over the ranks; token rows are read and results added across NVLink
+by the expert kernels themselves (peer memory; VK_EP_FORM=collective selects the NCCL all-to-all
+form). Strong scaling: the global batch is fixed. The same JSON line also carries the single-GPU decode sweep of the
 gpt-oss-20b-shaped layer (T in 1..128) with its HBM roofline.
 
 Prints ONE JSON line on rank 0. `--impl reference` times the reference's own CPU implementation
@@ -197,7 +198,8 @@ def run_reference_arm(args, cfg, T):
 def workload_config(cfg, T, n_gpus):
     return {"workload": f"{cfg.name}: T={T} H={cfg.H} I={cfg.I} E={cfg.E}+{cfg.shared_experts} top{cfg.top_k} "
                         f"{cfg.routing}", "tokens": T, "hidden": cfg.H, "ispp": cfg.I, "experts": cfg.E,
-            "top_k": cfg.top_k, "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus} (experts split, NCCL all-to-all)",
+            "top_k": cfg.top_k, "parallelism": "single GPU" if n_gpus == 1 else
+            f"ep{n_gpus} (experts split; token rows and results cross NVLink inside the kernels, NCCL all-to-all as fallback)",
             "weights": "MXFP4, 12 finite E2M1 codes uniform, ue8m0 exponent uniform in "
                        f"[{cfg.scale_exp[0]},{cfg.scale_exp[1]}]",
             "l2": "expert weights touched per step exceed the 126 MB L2"}
