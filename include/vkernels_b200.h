@@ -198,6 +198,28 @@ int vk_cuda_moe_ep_pack(const uint16_t* x, const int32_t* topk_ids, const float*
 int vk_cuda_moe_ep_combine(const float* recv_rows, const int32_t* row_of, int T, int H, int world,
                            uint16_t* out_bf16, float* out_f32, void* stream);
 
+/* The layer in four stages for tensor parallelism: counterparts of the reference's
+ * hip::moe_gateup_preact / moe_act_epilogue / moe_down_preact / moe_combine
+ * (src/c/vkernels/kernels/moe_fused.hpp:265-286), same argument lists plus the stream, status
+ * code returned. w13 / w2 are the rank's K-shards ([E, 2*ispp, hidden_k/2], [E, hidden,
+ * ispp_k/2], scales accordingly; hidden_k, ispp_k, k_base multiples of 64), k_base is the first
+ * column of A / act the shard covers; the caller all-reduces gate_up and partial over the ranks
+ * between the stages and passes the biases only to the element-wise stages. Blocks of 16 rows.
+ *   gate_up [EM, 2*ispp] fp32 (overwritten for rows of used blocks), act [EM, ispp] bf16
+ *   (padding rows not written), partial [EM, hidden] fp32, out [M, hidden] fp32 (accumulated). */
+int vk_cuda_moe_gateup_preact(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                              const int32_t* sorted_ids, const int32_t* expert_ids, float* gate_up, int M,
+                              int hidden, int ispp, int top_k, int EM, int k_base, int hidden_k, void* stream);
+int vk_cuda_moe_act_epilogue(const float* gate_up, const float* b13, uint16_t* act, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, int M, int top_k, int EM, int ispp, float swiglu_limit,
+                             int activation, float beta, float linear_beta, void* stream);
+int vk_cuda_moe_down_preact(const uint16_t* act, const uint8_t* w2, const uint8_t* w2_scale,
+                            const int32_t* sorted_ids, const int32_t* expert_ids, float* partial, int M, int ispp,
+                            int hidden, int top_k, int EM, int k_base, int ispp_k, void* stream);
+int vk_cuda_moe_combine(const float* partial, const float* b2, const float* topk_w_sorted,
+                        const int32_t* sorted_ids, const int32_t* expert_ids, float* out, int M, int hidden,
+                        int top_k, int EM, void* stream);
+
 /* Peer-memory form of expert parallelism (no reference counterpart: the reference moves token
  * rows and partial results through its collective, dist_moe.cpp:276-328). Only routing records
  * travel through the collective; the expert kernels read each token row and add each result in

@@ -131,3 +131,34 @@ def test_ep_plan_matches_oracle(oracle_mod):
         assert expert_begins(E, ep)[-1] == E
     with pytest.raises(ValueError):
         ep_plan(4, 8, 0)
+
+
+def test_tp_plan_geometry_and_rejections():
+    """Shard geometry of the tensor-parallel split (reference moe_tp_plan, dist_moe.hpp:61-81; its
+    own example: hidden 7168 and ispp 3072 at tp = 8 give 896 and 384)."""
+    from vkernels_b200.dist import tp_plan
+    p = tp_plan(7168, 3072, 8)
+    assert (p["hidden_shard"], p["ispp_shard"]) == (896, 384)
+    assert p["w13_shard_bytes"] == 2 * 3072 * 448 and p["w13s_shard_bytes"] == 2 * 3072 * 28
+    assert p["w2_shard_bytes"] == 7168 * 192 and p["w2s_shard_bytes"] == 7168 * 12
+    assert tp_plan(512, 256, 1)["hidden_shard"] == 512
+    for bad in [(512, 256, 0), (512, 256, 3), (2880, 2880, 2), (512, 256, 8)]:   # 1440, 64/32: not multiples of 64
+        with pytest.raises(ValueError):
+            tp_plan(*bad)
+
+
+def test_tp_shards_are_column_slices():
+    from vkernels_b200.dist import tp_plan, tp_shard_weights
+    E, H, I = 3, 256, 128
+    g = torch.Generator().manual_seed(1)
+    w13 = torch.randint(0, 256, (E, 2 * I, H // 2), dtype=torch.uint8, generator=g)
+    s13 = torch.randint(0, 256, (E, 2 * I, H // 32), dtype=torch.uint8, generator=g)
+    w2 = torch.randint(0, 256, (E, H, I // 2), dtype=torch.uint8, generator=g)
+    s2 = torch.randint(0, 256, (E, H, I // 32), dtype=torch.uint8, generator=g)
+    plan = tp_plan(H, I, 2)
+    parts = [tp_shard_weights(w13, s13, w2, s2, plan, r) for r in range(2)]
+    assert torch.equal(torch.cat([p["w13"] for p in parts], 2), w13)
+    assert torch.equal(torch.cat([p["w13_scale"] for p in parts], 2), s13)
+    assert torch.equal(torch.cat([p["w2"] for p in parts], 2), w2)
+    assert torch.equal(torch.cat([p["w2_scale"] for p in parts], 2), s2)
+    assert all(p["w13"].is_contiguous() and p["w2_scale"].is_contiguous() for p in parts)

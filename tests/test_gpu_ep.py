@@ -99,3 +99,50 @@ def test_expert_parallel_ranks_match_single_rank(world, tmp_path, oracle_mod):
     for r in range(world):
         txt = (tmp_path / f"rank{r}.txt").read_text()
         assert txt.startswith("1"), f"rank {r}: {txt}"
+
+
+def _tp_worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    try:
+        from vkernels_b200 import synthetic as syn
+        from vkernels_b200.dist import TensorParallelMoE, tp_plan, tp_shard_weights
+        from vkernels_b200.experts import layer_from_config
+
+        cfg = syn.scaled(syn.CONFIGS["c0"], E=6, top_k=3)   # H = 512, I = 256: shards of 256 and 128
+        T = 96
+        w = syn.make_expert_weights(cfg, backend="torch", device=dev)
+        A = syn.make_activations(cfg, T, backend="torch", device=dev, seed=cfg.seed)
+        full = layer_from_config(cfg, w, syn.make_router(cfg, device=dev), max_tokens=T)
+        ids, tw = full.route(A)
+        ids, tw = ids.clone(), tw.clone()
+        want = full.experts(A, ids, tw, return_fp32=True).clone()
+        shards = tp_shard_weights(w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], tp_plan(cfg.H, cfg.I, world), rank)
+        tp = TensorParallelMoE(shards, hidden=cfg.H, ispp=cfg.I, num_experts=cfg.E, top_k=cfg.top_k, rank=rank,
+                               world=world, swiglu_limit=cfg.swiglu_limit)
+        got = tp(A, ids, tw)
+        torch.cuda.synchronize()
+        err = float((got - want).abs().max())
+        scale = max(float(want.abs().max()), 1.0)
+        ok = err <= 2 ** -7 * scale   # the sum over K is split in two and the bf16 activation rounds once on both paths
+        open(os.path.join(tmp, f"rank{rank}.txt"), "w").write(f"{int(ok)} err={err} scale={scale}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_two_ranks_match_single_rank(tmp_path, oracle_mod):
+    """The stage split under a real all-reduce: two NCCL ranks with K-sharded weights reproduce the
+    single-rank layer (reference tests/kernels/moe/test_dist_moe.cpp:277-330)."""
+    import torch.multiprocessing as mp
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        txt = (tmp_path / f"rank{r}.txt").read_text()
+        assert txt.startswith("1"), f"rank {r}: {txt}"

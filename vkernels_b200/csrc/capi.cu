@@ -313,6 +313,43 @@ int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, con
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 
+/* ---------------- tensor-parallel stage split (device pointers) --------- */
+
+int vk_cuda_moe_gateup_preact(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
+                              const int32_t* sorted_ids, const int32_t* expert_ids, float* gate_up, int M,
+                              int hidden, int ispp, int top_k, int EM, int k_base, int hidden_k, void* stream) {
+  VK_TRY
+  vkc::moe_gateup_preact(A, w13, w13_scale, sorted_ids, expert_ids, gate_up, M, hidden, ispp, top_k, EM, k_base,
+                         hidden_k, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_act_epilogue(const float* gate_up, const float* b13, uint16_t* act, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, int M, int top_k, int EM, int ispp, float swiglu_limit,
+                             int activation, float beta, float linear_beta, void* stream) {
+  VK_TRY
+  vkc::moe_act_epilogue(gate_up, b13, act, sorted_ids, expert_ids, M, top_k, EM, ispp, swiglu_limit, activation,
+                        beta, linear_beta, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_down_preact(const uint16_t* act, const uint8_t* w2, const uint8_t* w2_scale,
+                            const int32_t* sorted_ids, const int32_t* expert_ids, float* partial, int M, int ispp,
+                            int hidden, int top_k, int EM, int k_base, int ispp_k, void* stream) {
+  VK_TRY
+  vkc::moe_down_preact(act, w2, w2_scale, sorted_ids, expert_ids, partial, M, ispp, hidden, top_k, EM, k_base,
+                       ispp_k, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_combine(const float* partial, const float* b2, const float* topk_w_sorted,
+                        const int32_t* sorted_ids, const int32_t* expert_ids, float* out, int M, int hidden,
+                        int top_k, int EM, void* stream) {
+  VK_TRY
+  vkc::moe_combine(partial, b2, topk_w_sorted, sorted_ids, expert_ids, out, M, hidden, top_k, EM, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
 /* ---------------- host entry points (HOST pointers) --------------------- */
 
 size_t vk_moe_align_block_size_max_em(int32_t M, int32_t top_k, int32_t block_size,

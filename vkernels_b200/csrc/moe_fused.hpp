@@ -74,6 +74,26 @@ void fused_moe_mxfp4_rows(const uint16_t* const* a_rows, const uint8_t* w13, con
                           float swiglu_limit, int activation, float beta, float linear_beta,
                           const float* b13, const float* b2, int block_size, void* stream);
 
+// The layer in four stages for tensor parallelism (reference moe_fused.hpp:265-286, same
+// argument lists plus the stream): w13 / w2 are this rank's K-shards ([E, 2*ispp, hidden_k/2] and
+// [E, hidden, ispp_k/2], scales accordingly), k_base is the first column of A / act the shard
+// covers, biases are applied after the caller's all-reduce. Token blocks are 16 rows.
+//   gate_up [EM, 2*ispp] fp32 <- moe_gateup_preact   (caller all-reduces)
+//   act     [EM, ispp]   bf16 <- moe_act_epilogue    (padding rows not written)
+//   partial [EM, hidden] fp32 <- moe_down_preact     (caller all-reduces)
+//   out     [M, hidden]  fp32 <- moe_combine         (accumulates; zero it first)
+void moe_gateup_preact(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const int32_t* sorted_ids,
+                       const int32_t* expert_ids, float* gate_up, int M, int hidden, int ispp, int top_k, int EM,
+                       int k_base, int hidden_k, void* stream = nullptr);
+void moe_act_epilogue(const float* gate_up, const float* b13, uint16_t* act, const int32_t* sorted_ids,
+                      const int32_t* expert_ids, int M, int top_k, int EM, int ispp, float swiglu_limit,
+                      int activation, float beta, float linear_beta, void* stream = nullptr);
+void moe_down_preact(const uint16_t* act, const uint8_t* w2, const uint8_t* w2_scale, const int32_t* sorted_ids,
+                     const int32_t* expert_ids, float* partial, int M, int ispp, int hidden, int top_k, int EM,
+                     int k_base, int ispp_k, void* stream = nullptr);
+void moe_combine(const float* partial, const float* b2, const float* topk_w_sorted, const int32_t* sorted_ids,
+                 const int32_t* expert_ids, float* out, int M, int hidden, int top_k, int EM, void* stream = nullptr);
+
 // Device alignment, any N = M*top_k (the reference stops at 1024). Output is
 // bit-identical to the host `moe_align_block_size`: experts ascending, flat
 // index ascending inside an expert, each expert padded to block_size with N,

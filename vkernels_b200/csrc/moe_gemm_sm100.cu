@@ -107,6 +107,9 @@ struct GemmParams {
   uint16_t* act;              // gate/up output [EM, n_feat]
   float* out;                 // down output [M, n_feat]
   float* const* out_rows;     // optional: address of each token's output row (may be another GPU's memory)
+  float* raw;                 // optional: plain fp32 result rows [EM, raw_ld] instead of the fused epilogue
+  int raw_ld;                 //   (the tensor-parallel stage split: the caller reduces across ranks first)
+  int k_base;                 // first column of the token rows this launch reduces over (K-sharded weights)
   const TokTile* tiles;
   const int* n_tiles;
   int* status;                // device status word (0 = ok)
@@ -675,7 +678,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (leader) mbar_expect_tx(bar, 2 * (h0 + h1) * 128 * n_slices);
             for (int sl = 0; sl < n_slices; ++sl) {
               const uint32_t d = dst + sl * slice_bytes;
-              const int k0 = st * KS + sl * 64;
+              const int k0 = p.k_base + st * KS + sl * 64;
               int r = 0;
               for (; r + 64 <= h0; r += 64) tma_load_2d_pair(d + r * 128, &tmap_b64, k0, row_main + r, bar);
               for (; r < h0; r += 16) tma_load_2d_pair(d + r * 128, &tmap_b, k0, row_main + r, bar);
@@ -707,9 +710,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           for (int sl = 0; sl < n_slices; ++sl) {
             int r = 0;
             for (; r + 64 <= tt.n_rows; r += 64)
-              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, k0 + sl * 64, tt.row0 + r, bar);
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b64, p.k_base + k0 + sl * 64, tt.row0 + r, bar);
             for (; r < tt.n_rows; r += 16)
-              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, k0 + sl * 64, tt.row0 + r, bar);
+              tma_load_2d(dst + sl * slice_bytes + r * 128, &tmap_b, p.k_base + k0 + sl * 64, tt.row0 + r, bar);
           }
           b.advance(p.b_stages);
         }
@@ -946,7 +949,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           float* orow = p.out_rows ? p.out_rows[token] : p.out + (size_t)token * p.n_feat;
           bars->tile_ref[j] = real ? reinterpret_cast<unsigned long long>(orow) : 0ull;
         }
-        if (!GATEUP) bars->tile_w[j] = real ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
+        if (!GATEUP) bars->tile_w[j] = (real && p.topk_w != nullptr) ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
       named_bar_sync(1, 128 * kEpiSets);
       if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256)) break;
@@ -983,6 +986,23 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           tc_ld_16x256b_x4(t_lane + (16u << 16) + c0, vb);
           tc_wait_ld();
           if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
+          if (p.raw != nullptr) {   // stage split: pre-activation sums, gate columns then up columns
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int t = c0 + 8 * i + tk + e;
+                if (t < tt.n_rows) {
+                  float* d = p.raw + (size_t)(tt.row0 + t) * p.raw_ld + f * 64 + fl;
+                  d[0] = __uint_as_float(va[4 * i + e]);
+                  d[p.n_feat] = __uint_as_float(va[4 * i + 2 + e]);
+                  d[8] = __uint_as_float(vb[4 * i + e]);
+                  d[p.n_feat + 8] = __uint_as_float(vb[4 * i + 2 + e]);
+                }
+              }
+            }
+            continue;
+          }
           // which of the round's 32 tokens are real rows: one shared-memory read per lane and
           // a ballot, so the stores below depend on no load
           const int my_t = c0 + lane;
@@ -1049,6 +1069,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
               for (int i = 0; i < 4; ++i) {
                 const int tl = (lane >> 3) + 4 * i;
                 const int t = c0 + half * 16 + tl;
+                if (p.raw != nullptr) {   // stage split: plain partial rows, no bias, no routing weight
+                  if (t < tt.n_rows && quad_ok)
+                    *reinterpret_cast<float4*>(p.raw + (size_t)(tt.row0 + t) * p.raw_ld + h0) =
+                        *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                  continue;
+                }
                 float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
                 if (orow != nullptr && quad_ok) {
                   const float wgt = bars->tile_w[t];
@@ -1427,6 +1453,43 @@ int sm100_last_status() {
   return v;
 }
 
+
+namespace {
+// Largest token tile of a launch and whether the CTA-pair form runs it.
+struct TileChoice {
+  int max_tok;
+  bool use_pair;
+};
+TileChoice choose_tiles(int M, int top_k, int EM, int block_size, int k_gateup, int k_down) {
+  // A token meets an expert at most once, so no expert holds more than M rows (+ padding).
+  int max_tok = ((M + block_size - 1) / block_size) * block_size;
+  max_tok = ((max_tok + 15) / 16) * 16;
+  // When an expert sees a few dozen tokens at most, tiles are capped at 64 rows so that the launch
+  // takes the long-stage form built for small tiles (an expert with more rows is split into
+  // several items); measured crossover against the CTA-pair form: about 48 tokens per expert.
+  // The expert count is not an argument of the layer: callers size EM as N + E * (block - 1),
+  // which gives a lower bound of E (an exact EM only makes the estimate more conservative).
+  {
+    const long long n_slots = (long long)M * top_k;
+    const long long e_est = std::max<long long>(1, ((long long)EM - n_slots) / (block_size - 1));
+    if ((M <= 256 || n_slots <= 48 * e_est) && max_tok > 64) max_tok = 64;
+  }
+  // Tiles over 128 tokens go to CTA pairs when both GEMMs fit shared memory in that form.
+  bool use_pair = false;
+  if (max_tok > 128 && pair_mode()) {
+    GemmParams probe{};
+    probe.max_tok = max_tok > kPairMaxTok ? kPairMaxTok : ((max_tok + 31) & ~31);
+    probe.K = k_gateup;
+    use_pair = pair_fits(probe, true);
+    probe.K = k_down;
+    use_pair = use_pair && pair_fits(probe, false);
+    if (use_pair) max_tok = probe.max_tok;   // a CTA pair stages half of the rows each
+  }
+  if (!use_pair && max_tok > kMaxTok) max_tok = kMaxTok;
+  return TileChoice{max_tok, use_pair};
+}
+}  // namespace
+
 void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
                       const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
                       int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
@@ -1450,31 +1513,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // The number of experts is not an argument of the layer; the tensor maps
   // cover the rows of every expert id that fits an int32 row index.
   const uint64_t w13_rows_cap = (uint64_t)1 << 31;
-  // A token meets an expert at most once, so no expert holds more than M rows (+ padding).
-  int max_tok = ((M + block_size - 1) / block_size) * block_size;
-  max_tok = ((max_tok + 15) / 16) * 16;
-  // When an expert sees a few dozen tokens at most, tiles are capped at 64 rows so that the launch
-  // takes the long-stage form built for small tiles (an expert with more rows is split into
-  // several items); measured crossover against the CTA-pair form: about 48 tokens per expert.
-  // The expert count is not an argument of the layer: callers size EM as N + E * (block - 1),
-  // which gives a lower bound of E (an exact EM only makes the estimate more conservative).
-  {
-    const long long n_slots = (long long)M * top_k;
-    const long long e_est = std::max<long long>(1, ((long long)EM - n_slots) / (block_size - 1));
-    if ((M <= 256 || n_slots <= 48 * e_est) && max_tok > 64) max_tok = 64;
-  }
-  // Tiles over 128 tokens go to CTA pairs when both GEMMs fit shared memory in that form.
-  bool use_pair = false;
-  if (max_tok > 128 && pair_mode()) {
-    GemmParams probe{};
-    probe.max_tok = max_tok > kPairMaxTok ? kPairMaxTok : ((max_tok + 31) & ~31);
-    probe.K = hidden;
-    use_pair = pair_fits(probe, true);
-    probe.K = ispp;
-    use_pair = use_pair && pair_fits(probe, false);
-    if (use_pair) max_tok = probe.max_tok;   // a CTA pair stages half of the rows each
-  }
-  if (!use_pair && max_tok > kMaxTok) max_tok = kMaxTok;
+  const TileChoice choice = choose_tiles(M, top_k, EM, block_size, hidden, ispp);
+  const int max_tok = choice.max_tok;
+  const bool use_pair = choice.use_pair;
   build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                              n_tiles, max_tok_tiles(EM));
   gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM,
@@ -1511,6 +1552,66 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                                       (uint64_t)ispp * 2, 64, 64);
     launch_gemm<false>(tw, tb, tb64, p, use_pair, stream);
     timer_mark(2, stream);
+  }
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+// One GEMM of the tensor-parallel stage split (reference moe_fused.hpp:265-286): this rank's
+// weights are a K-shard ([E, rows, k_shard/2] packed, [E, rows, k_shard/32] scales), the token
+// rows are full width and are read from column k_base on; the result is the plain fp32 partial
+// sum (no bias, activation or routing weight), which the caller all-reduces over the ranks.
+//   which = 0: gate_up[EM, 2*n_out] = gather(A[M, k_full]) @ w13_shard^T     (n_out = ispp)
+//   which = 1: partial[EM, n_out]   = act[EM, k_full]      @ w2_shard^T      (n_out = hidden)
+// Rows of blocks with expert_ids < 0 are left untouched, padding rows of real blocks become 0.
+void launch_moe_stage_gemm(int which, const uint16_t* rows_in, const uint8_t* w, const uint8_t* w_scale,
+                           const int32_t* sorted_ids, const int32_t* expert_ids, float* raw, int M,
+                           int k_full, int n_out, int top_k, int EM, int k_base, int k_shard,
+                           cudaStream_t stream) {
+  constexpr int block_size = 16;
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  expects(which == 0 || which == 1, "moe stage: unknown stage");
+  expects(M >= 0 && EM >= 0 && top_k > 0 && EM % block_size == 0, "moe stage: bad M / EM / top_k");
+  expects(k_full > 0 && k_full % 64 == 0 && n_out > 0 && n_out % 64 == 0, "moe stage: dimensions must be multiples of 64");
+  expects(k_shard > 0 && k_shard % 64 == 0 && k_base >= 0 && k_base % 64 == 0 && k_base + k_shard <= k_full,
+          "moe stage: the K shard must be a multiple of 64 inside the full reduction length");
+  if (M == 0 || EM == 0) return;
+  expects(rows_in && w && w_scale && sorted_ids && expert_ids && raw, "moe stage: buffers must not be null");
+  expects(aligned16(rows_in) && aligned16(w) && aligned16(w_scale) && aligned16(raw),
+          "moe stage: buffers must be 16-byte aligned");
+  const WsLayout l = ws_layout(EM, which == 0 ? k_full : 64);
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total));
+  TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
+  int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);
+  int* status = reinterpret_cast<int*>(ws + l.status_off);
+  uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
+  const TileChoice choice = choose_tiles(M, top_k, EM, block_size, k_shard, k_shard);
+  build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, choice.max_tok, tiles,
+                                             n_tiles, max_tok_tiles(EM));
+  const uint16_t* token_rows = rows_in;
+  if (which == 0) {
+    gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(rows_in, nullptr, sorted_ids, expert_ids, block_size, EM,
+                                                         M * top_k, top_k, k_full, gathered);
+    token_rows = gathered;
+  }
+  GemmParams p{};
+  p.sorted_ids = sorted_ids; p.tiles = tiles; p.n_tiles = n_tiles; p.status = status;
+  p.N = M * top_k; p.top_k = top_k; p.max_tok = choice.max_tok;
+  p.w_scale = w_scale; p.K = k_shard; p.k_base = k_base; p.raw = raw;
+  p.n_feat = n_out;
+  const uint64_t rows_cap = (uint64_t)1 << 31;
+  const CUtensorMap tw = make_map(w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k_shard / 2, rows_cap, k_shard / 2, 128, 64);
+  const CUtensorMap tb = make_map(token_rows, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_full, EM,
+                                  (uint64_t)k_full * 2, 64, 16);
+  const CUtensorMap tb64 = make_map(token_rows, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_full, EM,
+                                    (uint64_t)k_full * 2, 64, 64);
+  if (which == 0) {
+    p.n_ftiles = n_out / 64;
+    p.raw_ld = 2 * n_out;
+    launch_gemm<true>(tw, tb, tb64, p, choice.use_pair, stream);
+  } else {
+    p.n_ftiles = (n_out + 127) / 128;
+    p.raw_ld = n_out;
+    launch_gemm<false>(tw, tb, tb64, p, choice.use_pair, stream);
   }
   VK_CUDA_CHECK(cudaGetLastError());
 }

@@ -56,6 +56,84 @@ def expert_begins(num_experts: int, ep: int) -> list[int]:
     return [ep_plan(num_experts, ep, r)[0] for r in range(ep)] + [num_experts]
 
 
+# ---------------------------------------------------------------------------------------------
+# tensor parallelism (weights sharded along the reduction dimensions)
+# ---------------------------------------------------------------------------------------------
+
+def tp_plan(hidden: int, ispp: int, tp: int) -> dict:
+    """Shard geometry of one tensor-parallel rank (reference dist_moe.hpp:61-81, ``moe_tp_plan``):
+    w13 is cut along hidden, w2 along ispp; both shards must stay multiples of 64."""
+    if tp <= 0 or hidden % tp or ispp % tp:
+        raise ValueError("tp_plan: tp must be positive and divide hidden and ispp")
+    hs, ish = hidden // tp, ispp // tp
+    if hs % 64 or ish % 64:
+        raise ValueError("tp_plan: hidden / tp and ispp / tp must be multiples of 64")
+    return {"tp": tp, "hidden": hidden, "ispp": ispp, "hidden_shard": hs, "ispp_shard": ish,
+            "w13_shard_bytes": 2 * ispp * (hs // 2), "w13s_shard_bytes": 2 * ispp * (hs // 32),
+            "w2_shard_bytes": hidden * (ish // 2), "w2s_shard_bytes": hidden * (ish // 32)}
+
+
+def tp_shard_weights(w13, w13_scale, w2, w2_scale, plan: dict, rank: int) -> dict:
+    """Rank ``rank``'s contiguous column slices of the packed weights and scales (reference
+    ``moe_tp_shard_w13`` / ``moe_tp_shard_w2``, dist_moe.hpp:83-98); biases stay whole."""
+    hs, ish = plan["hidden_shard"], plan["ispp_shard"]
+    return {"w13": w13[:, :, rank * hs // 2:(rank + 1) * hs // 2].contiguous(),
+            "w13_scale": w13_scale[:, :, rank * hs // 32:(rank + 1) * hs // 32].contiguous(),
+            "w2": w2[:, :, rank * ish // 2:(rank + 1) * ish // 2].contiguous(),
+            "w2_scale": w2_scale[:, :, rank * ish // 32:(rank + 1) * ish // 32].contiguous()}
+
+
+class TensorParallelMoE:
+    """One rank of the tensor-parallel layer (reference ``fused_moe_mxfp4_tp_rank``,
+    dist_moe.hpp:100-131): activations and routing are replicated, the rank holds K-shards of
+    the weights, and the two partial results are all-reduced over the group between the stages:
+
+        gate/up partial sums -> all-reduce -> bias + activation -> down partial sums
+        -> all-reduce -> bias, routing weight, combine
+
+    CUDA only (NCCL all-reduce on the current stream)."""
+
+    def __init__(self, shards: dict, *, hidden: int, ispp: int, num_experts: int, top_k: int, rank: int, world: int,
+                 group=None, b13=None, b2=None, swiglu_limit: float = 0.0, activation: int = 0, beta: float = 4.0,
+                 linear_beta: float = 25.0):
+        self.plan = tp_plan(hidden, ispp, world)
+        self.w = shards
+        self.hidden, self.ispp, self.num_experts, self.top_k = hidden, ispp, num_experts, top_k
+        self.rank, self.world, self.group = rank, world, group
+        self.b13, self.b2 = b13, b2
+        self.swiglu_limit, self.activation, self.beta, self.linear_beta = swiglu_limit, activation, beta, linear_beta
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+        """x [T, hidden] bf16 (the same on every rank), routing [T, k] -> fp32 [T, hidden] (the same
+        on every rank)."""
+        from . import torch_ops as ops
+
+        T = x.shape[0]
+        dev = x.device
+        sids, eids, _ = ops.moe_align_block_size(topk_ids, self.num_experts, 16)
+        EM = sids.numel()
+        flat = sids.long().clamp(max=T * self.top_k - 1)
+        tws = torch.where(sids < T * self.top_k, topk_w.reshape(-1)[flat], torch.zeros((), device=dev))
+        hs, ish = self.plan["hidden_shard"], self.plan["ispp_shard"]
+        gate_up = torch.zeros((EM, 2 * self.ispp), dtype=torch.float32, device=dev)
+        ops.moe_gateup_preact(x, self.w["w13"], self.w["w13_scale"], sids, eids, gate_up, top_k=self.top_k,
+                              k_base=self.rank * hs)
+        dist.all_reduce(gate_up, group=self.group)
+        act = torch.zeros((EM, self.ispp), dtype=torch.bfloat16, device=dev)
+        ops.moe_act_epilogue(gate_up, act, sids, eids, M=T, top_k=self.top_k, b13=self.b13,
+                             swiglu_limit=self.swiglu_limit, activation=self.activation, beta=self.beta,
+                             linear_beta=self.linear_beta)
+        partial = torch.zeros((EM, self.hidden), dtype=torch.float32, device=dev)
+        ops.moe_down_preact(act, self.w["w2"], self.w["w2_scale"], sids, eids, partial, M=T, top_k=self.top_k,
+                            k_base=self.rank * ish)
+        dist.all_reduce(partial, group=self.group)
+        out = torch.zeros((T, self.hidden), dtype=torch.float32, device=dev)
+        ops.moe_combine(partial, tws.contiguous(), sids, eids, out, top_k=self.top_k, b2=self.b2)
+        return out
+
+    __call__ = forward
+
+
 class CudaBackend:
     """Device steps of the EP layer on the CUDA library."""
 

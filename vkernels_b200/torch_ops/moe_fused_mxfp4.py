@@ -220,6 +220,65 @@ def fused_moe_mxfp4_rows_into(act_scratch, a_rows, out_rows, w13, w13_scale, w2,
     nr.check(rc, "fused_moe_mxfp4_rows")
 
 
+# ---- the layer in four stages (tensor parallelism): see include/vkernels_b200.h -------------------
+
+def moe_gateup_preact(A, w13_shard, w13_scale_shard, sorted_ids, expert_ids, gate_up, *, top_k: int, k_base: int = 0):
+    """gate_up [EM, 2*ispp] fp32 = gather(A)[:, k_base : k_base + hidden_k] @ w13_shard^T (no bias, no
+    activation); ``w13_shard`` is [E, 2*ispp, hidden_k/2]. The caller adds the ranks' results."""
+    same_gpu_contiguous(A, w13_shard, w13_scale_shard, sorted_ids, expert_ids, gate_up)
+    M, hidden = A.shape
+    ispp, hidden_k = w13_shard.shape[1] // 2, w13_shard.shape[2] * 2
+    EM = sorted_ids.numel()
+    require(gate_up.dtype == torch.float32 and gate_up.shape == (EM, 2 * ispp), "gate_up must be fp32 [EM, 2*ispp]")
+    with torch.cuda.device(A.device):
+        nr.check(nr.load_library().vk_cuda_moe_gateup_preact(
+            _ptr(A), _ptr(w13_shard), _ptr(w13_scale_shard), _ptr(sorted_ids), _ptr(expert_ids), _ptr(gate_up), M,
+            hidden, ispp, top_k, EM, k_base, hidden_k, _stream(A)), "moe_gateup_preact")
+    return gate_up
+
+
+def moe_act_epilogue(gate_up, act, sorted_ids, expert_ids, *, M: int, top_k: int, b13=None, swiglu_limit: float = 0.0,
+                     activation: int = SWIGLU, beta: float = 4.0, linear_beta: float = 25.0):
+    """act [EM, ispp] bf16 = activation(gate_up + b13), one rounding; padding rows are not written."""
+    same_gpu_contiguous(gate_up, act, sorted_ids, expert_ids, *([b13] if b13 is not None else []))
+    EM, ispp = act.shape
+    require(gate_up.shape == (EM, 2 * ispp) and act.dtype == torch.bfloat16, "gate_up fp32 [EM, 2*ispp], act bf16 [EM, ispp]")
+    with torch.cuda.device(act.device):
+        nr.check(nr.load_library().vk_cuda_moe_act_epilogue(
+            _ptr(gate_up), _ptr(b13), _ptr(act), _ptr(sorted_ids), _ptr(expert_ids), M, top_k, EM, ispp,
+            float(swiglu_limit), int(activation), float(beta), float(linear_beta), _stream(act)), "moe_act_epilogue")
+    return act
+
+
+def moe_down_preact(act, w2_shard, w2_scale_shard, sorted_ids, expert_ids, partial, *, M: int, top_k: int,
+                    k_base: int = 0):
+    """partial [EM, hidden] fp32 = act[:, k_base : k_base + ispp_k] @ w2_shard^T; ``w2_shard`` is
+    [E, hidden, ispp_k/2]. The caller adds the ranks' results."""
+    same_gpu_contiguous(act, w2_shard, w2_scale_shard, sorted_ids, expert_ids, partial)
+    EM, ispp = act.shape
+    hidden, ispp_k = w2_shard.shape[1], w2_shard.shape[2] * 2
+    require(partial.dtype == torch.float32 and partial.shape == (EM, hidden), "partial must be fp32 [EM, hidden]")
+    with torch.cuda.device(act.device):
+        nr.check(nr.load_library().vk_cuda_moe_down_preact(
+            _ptr(act), _ptr(w2_shard), _ptr(w2_scale_shard), _ptr(sorted_ids), _ptr(expert_ids), _ptr(partial), M,
+            ispp, hidden, top_k, EM, k_base, ispp_k, _stream(act)), "moe_down_preact")
+    return partial
+
+
+def moe_combine(partial, topk_w_sorted, sorted_ids, expert_ids, out, *, top_k: int, b2=None):
+    """out [M, hidden] fp32 += (partial + b2) * topk_w_sorted per real row (zero ``out`` first)."""
+    same_gpu_contiguous(partial, topk_w_sorted, sorted_ids, expert_ids, out, *([b2] if b2 is not None else []))
+    EM, hidden = partial.shape
+    M = out.shape[0]
+    require(out.dtype == torch.float32 and out.shape[1] == hidden and topk_w_sorted.numel() >= EM,
+            "out fp32 [M, hidden], topk_w_sorted [EM]")
+    with torch.cuda.device(out.device):
+        nr.check(nr.load_library().vk_cuda_moe_combine(
+            _ptr(partial), _ptr(b2), _ptr(topk_w_sorted), _ptr(sorted_ids), _ptr(expert_ids), _ptr(out), M, hidden,
+            top_k, EM, _stream(out)), "moe_combine")
+    return out
+
+
 def fused_moe_mxfp4(hidden_states, w13, w13_scale, w2, w2_scale, topk_ids, topk_weights, *,
                     swiglu_limit: float = 0.0, activation: int = SWIGLU, beta: float = 4.0,
                     linear_beta: float = 25.0, b13=None, b2=None, expert_map=None,
