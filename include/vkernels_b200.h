@@ -156,15 +156,38 @@ int vk_cuda_moe_route_topk(const float* logits, const float* bias, int T, int E,
 int vk_cuda_moe_set_impl(int impl);
 int vk_cuda_moe_get_impl(void);
 
-/* The library keeps one grow-only scratch block per device (alignment
- * histograms, tile lists, gathered activation rows). Growing it calls
- * cudaMalloc: reserve the largest problem once, before any stream capture. */
+/* Library scratch (alignment histograms, tile lists, gathered activation rows): one block per
+ * (device, stream). Layer and alignment calls on different streams therefore never share
+ * scratch and may run concurrently; calls on one stream are ordered by the stream. The
+ * launchers keep the reference's ownership rule (src/c/vkernels/kernels/moe_fused.hpp:296-307:
+ * no synchronisation, no free) with one exception: the FIRST call on a stream, or a call larger
+ * than everything before it on that stream, allocates the stream's block with cudaMalloc (the
+ * outgrown block stays alive for enqueued work and captured graphs until
+ * vk_cuda_moe_release_workspaces). vk_cuda_moe_reserve_workspace_on(bytes, stream) does that
+ * allocation ahead of time; with the block reserved the launchers allocate nothing. While
+ * `stream` is being captured an allocation is impossible: the call launches nothing and reports
+ * VK_ERROR_INVALID_ARGUMENT ("reserve ... before the capture").
+ * vk_cuda_moe_reserve_workspace(bytes) reserves for the default stream (NULL).
+ * vk_cuda_moe_release_workspaces frees all blocks of the current device: only when none of the
+ * library's work is pending and no captured graph using them will be replayed. */
 size_t vk_cuda_moe_workspace_bytes(int max_EM, int hidden, int ispp, int n_local_experts, int N);
 int vk_cuda_moe_reserve_workspace(size_t bytes);
+int vk_cuda_moe_reserve_workspace_on(size_t bytes, void* stream);
+int vk_cuda_moe_release_workspaces(void);
+size_t vk_cuda_moe_workspace_live_bytes(void);
 
-/* Synchronises the device and reports whether any tensor-core launch gave up
- * on one of its bounded waits (VK_ERROR_INTERNAL) - never expected. */
+/* Every wait inside the tensor-core kernels is bounded (about two seconds of SM clock); a wait
+ * that runs out makes its CTA free its tensor memory and return, and records 100 + the wait's
+ * code in a status word of the device. vk_cuda_moe_kernel_status synchronises the device and
+ * returns VK_ERROR_INTERNAL if the word is set (never expected); the word stays set until
+ * vk_cuda_moe_reset_kernel_status clears it (also synchronises). */
 int vk_cuda_moe_kernel_status(void);
+int vk_cuda_moe_reset_kernel_status(void);
+/* Test hook for that path: one warp waits with the kernels' own bounded wait on a barrier
+ * nobody arrives on and gives up after limit_clocks (1 .. 2e9) SM clocks, which sets the status
+ * word like a GEMM kernel would. It returns by itself; nothing hangs and no real launch is
+ * starved. */
+int vk_cuda_moe_test_wait_timeout(long long limit_clocks, void* stream);
 
 /* Device time of the two GEMM kernels, measured with events on the launch
  * stream around up to max_calls layer calls; _end synchronises and returns the
@@ -173,11 +196,15 @@ int vk_cuda_moe_kernel_status(void);
 int vk_cuda_moe_timing_begin(int max_calls);
 int vk_cuda_moe_timing_end(float* gateup_ms, float* down_ms, int* calls);
 
-/* out[rows,K] bf16 = dequantised packed[rows,K/2] x scale[rows,K/32], through
- * the device function the GEMM kernels use (reference definition
- * moe_fused.cpp:141-174). */
+/* out[rows,K] bf16 = dequantised packed[rows,K/2] x scale[rows,K/32] (reference definition
+ * moe_fused.cpp:141-174), through the device functions the GEMM kernels decode with:
+ * path 0 = the byte-permute decoder of the CTA-pair (prefill) form, path 1 = the shared-memory
+ * table decoder of the lone-CTA (decode) form (K % 64 == 0, 16-byte aligned buffers).
+ * vk_cuda_mxfp4_dequant_rows is path 0. */
 int vk_cuda_mxfp4_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
                                int rows, int K, void* stream);
+int vk_cuda_mxfp4_dequant_rows_path(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
+                                    int rows, int K, int path, void* stream);
 
 /* Expert parallelism (partition rule: src/c/vkernels/dist/dist_moe.cpp:225-274).
  * expert_begin [world+1]: first expert of each rank, last entry = E.
@@ -254,6 +281,16 @@ int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_cou
                                     int slots, const uint64_t* x_bases, const uint64_t* out_bases,
                                     int H, int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
                                     void* stream);
+/* Cross-rank barrier of the peer-memory form, run as a kernel on `stream`: flag_bases[d] is the
+ * address, in this process, of rank d's flag array ([8 slots][world] int32, zero at start, in
+ * memory every rank can address). The kernel publishes `epoch` into entry [slot][rank] of every
+ * rank's array (system-scope release, after a system-scope fence over this stream's earlier
+ * writes) and waits until every entry [slot][*] of its own array has reached `epoch` (acquire).
+ * Epochs must grow from call to call on a slot. The wait gives up after limit_clocks SM clocks
+ * (at most 8e9): the kernel then records 200 + the missing rank in a status word that
+ * vk_cuda_moe_kernel_status reports, and returns - a rank that left does not hang the others. */
+int vk_cuda_moe_ep_flag_barrier(const uint64_t* flag_bases, int world, int rank, int slot, int epoch,
+                                long long limit_clocks, void* stream);
 int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
                                  const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
                                  uint16_t* act_scratch, const uint64_t* out_rows, int M, int hidden,

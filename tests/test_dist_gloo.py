@@ -123,6 +123,57 @@ def test_ep_exchange_on_gloo_ranks(world, tmp_path, oracle_mod):
         assert txt.startswith("1"), f"rank {r}: {txt}"
 
 
+def _leaving_worker(rank, world, port, tmp):
+    """Rank `world - 1` runs one healthy step and then leaves between steps (no collective in
+    flight); the others start a second step and must get an error out of their exchange within
+    the process group's timeout instead of waiting forever."""
+    import datetime
+    import time
+
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from vkernels_b200 import synthetic as syn
+    from vkernels_b200.dist import ExpertParallelMoE
+
+    cfg = syn.scaled(syn.CONFIGS["c0"], H=128, I=64, E=6, top_k=2)
+    w = {k: v.numpy() for k, v in syn.make_expert_weights(cfg).items()}
+    A = syn.make_activations(cfg, 8 * world)
+    rng = np.random.default_rng(rank)
+    ids = torch.from_numpy(np.stack([rng.permutation(cfg.E)[: cfg.top_k] for _ in range(8)]).astype(np.int32))
+    tw = torch.from_numpy(rng.random((8, cfg.top_k), dtype=np.float32))
+    layer = ExpertParallelMoE(NumpyBackend(w, cfg.E, rank, world), num_experts=cfg.E, top_k=cfg.top_k,
+                              hidden=cfg.H, rank=rank, world=world)
+    x = A[rank * 8:(rank + 1) * 8].contiguous()
+    layer(x, topk=(ids, tw))                       # step 1: everybody is there
+    verdict = "left"
+    if rank != world - 1:
+        t0 = time.time()
+        try:
+            layer(x, topk=(ids, tw))               # step 2: one rank is gone
+            verdict = "no error"
+        except Exception as e:  # noqa: BLE001 - any error out of the exchange is the expected outcome
+            verdict = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+    open(os.path.join(tmp, f"rank{rank}.txt"), "w").write(verdict)
+    # no destroy_process_group: the group is broken on purpose; the process simply exits
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_steps_surfaces_as_an_error(tmp_path, oracle_mod):
+    world = 3
+    ctx = mp.spawn(_leaving_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=False)
+    deadline = 90
+    import time
+    t0 = time.time()
+    while not ctx.join(timeout=1.0):
+        assert time.time() - t0 < deadline, "ranks are still waiting for the one that left"
+    assert (tmp_path / f"rank{world - 1}.txt").read_text() == "left"
+    for r in range(world - 1):
+        txt = (tmp_path / f"rank{r}.txt").read_text()
+        assert txt.startswith("error after"), f"rank {r}: {txt}"
+
+
 def test_ep_plan_matches_oracle(oracle_mod):
     from vkernels_b200.dist import ep_plan, expert_begins
     for E, ep in [(8, 2), (7, 3), (128, 8), (257, 8), (5, 5)]:

@@ -231,11 +231,24 @@ def test_status_word_survives_the_alignment_scratch():
 
 
 def test_c3_shape_with_shared_expert_on_a_token_subsample():
+    """The DeepSeek-V3-shaped configuration at its stated batch (T = 16384, 256 routed experts
+    plus the always-on shared one, full-size weights); the oracle evaluates 64 seeded tokens."""
     cfg = syn.CONFIGS["c3"]
-    T = 4096   # the full T = 16384 runs in bench.py; the weights (5.7 GB) are full size here
+    T = 16384
     rng = np.random.default_rng(3)
     tokens = np.sort(rng.choice(T, 64, replace=False))
     _parity(cfg, T, impl="tcgen05", tokens=tokens, backend="torch")
+
+
+@pytest.mark.parametrize("T", [1, 16, 256])
+def test_c4_zipf_small_batches(T):
+    """The load-imbalance configuration at its small batch sizes (Zipf 1.2 expert popularity):
+    a few hot experts collect most tokens while the launch is still in the small-tile regime,
+    the sizes at which the tile cap and the form choice flip."""
+    cfg = syn.CONFIGS["c4"]
+    logits = syn.make_zipf_logits(cfg, T, device=DEV)
+    tokens = None if T <= 64 else np.sort(np.random.default_rng(T).choice(T, 64, replace=False))
+    _parity(cfg, T, impl="tcgen05", tokens=tokens, logits=logits, backend="torch")
 
 
 def test_full_size_properties_c2():

@@ -14,15 +14,17 @@ from vkernels_b200 import synthetic as syn  # noqa: E402
 from vkernels_b200 import torch_ops as ops  # noqa: E402
 
 
-def test_dequant_all_bytes_all_scales_bit_exact():
-    """Every (packed byte, scale byte) pair: the device decoder equals the CPU definition bit
-    for bit on finite values and agrees on which values are NaN
+@pytest.mark.parametrize("path", ["permute", "table"])
+def test_dequant_all_bytes_all_scales_bit_exact(path):
+    """Every (packed byte, scale byte) pair, through both decoders the GEMM kernels use (byte
+    permutes in the CTA-pair form, the shared-memory table in the lone-CTA form): equal to the CPU
+    definition bit for bit on finite values, same NaN positions
     (reference tests/kernels/moe/test_moe_fused.cpp:591-621)."""
     rows, K = 256, 512
     packed = (torch.arange(rows * K // 2, device=DEV) & 0xFF).to(torch.uint8).view(rows, K // 2)
     # row r uses scale byte r; every row contains every byte value
     scale = torch.arange(256, device=DEV, dtype=torch.uint8).view(rows, 1).expand(rows, K // 32).contiguous()
-    got = bf16_to_u16(ops.mxfp4_dequant_rows(packed, scale))
+    got = bf16_to_u16(ops.mxfp4_dequant_rows(packed, scale, path=path))
     ref = np.empty((rows, K), np.uint16)
     pk, sc = to_np(packed), to_np(scale)
     for r in range(rows):
@@ -32,11 +34,12 @@ def test_dequant_all_bytes_all_scales_bit_exact():
     assert np.array_equal(got[~nan_r], ref[~nan_r])
 
 
-def test_dequant_random_rows():
+@pytest.mark.parametrize("path", ["permute", "table"])
+def test_dequant_random_rows(path):
     g = torch.Generator(device=DEV).manual_seed(3)
     packed = torch.randint(0, 256, (64, 1440), generator=g, device=DEV, dtype=torch.uint8)
     scale = torch.randint(0, 256, (64, 90), generator=g, device=DEV, dtype=torch.uint8)
-    got = bf16_to_u16(ops.mxfp4_dequant_rows(packed, scale))
+    got = bf16_to_u16(ops.mxfp4_dequant_rows(packed, scale, path=path))
     ref = oracle.dequant_weight_tile(to_np(packed), to_np(scale), 64, 2880).T
     nan_r = np.isnan(oracle.bf16_to_f32(ref))
     assert np.array_equal(np.isnan(oracle.bf16_to_f32(got)), nan_r)

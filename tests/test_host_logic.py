@@ -1,6 +1,6 @@
 """Host-side pieces that need no GPU: the C ABI library loads and exports what the header
-declares, argument errors surface as status codes, persistent scratch refuses to grow during
-capture, the workload generator is reproducible."""
+declares, argument errors surface as status codes, the layer's step arena never reallocates,
+the workload generator is reproducible."""
 import os
 import re
 
@@ -10,7 +10,7 @@ import torch
 
 from vkernels_b200 import native_runtime as nr
 from vkernels_b200 import synthetic as syn
-from vkernels_b200.experts import CaptureSafeScratch, max_num_tokens_hint
+from vkernels_b200.experts import StepArena
 from vkernels_b200.torch_ops import OpNotEligible, fused_moe_mxfp4, moe_align_block_size
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -81,31 +81,26 @@ def test_missing_library_is_loud(monkeypatch):
         nr.load_library()
 
 
-def test_capture_safe_scratch_refuses_growth_during_capture():
-    """reference tests/python/test_vllm_experts.py:346-376."""
-    capturing = {"on": False}
-    s = CaptureSafeScratch(capture_probe=lambda: capturing["on"])
-    dev = torch.device("cpu")
-    a = s.get("out", 10, dtype=torch.float32, device=dev, capacity=100)
-    assert a.numel() == 10
-    b = s.get("out", 100, dtype=torch.float32, device=dev)
-    assert b.data_ptr() == a.data_ptr()          # sliced, not reallocated
-    capturing["on"] = True
-    assert s.get("out", 50, dtype=torch.float32, device=dev).numel() == 50
-    with pytest.raises(RuntimeError, match="refusing to grow"):
-        s.get("out", 101, dtype=torch.float32, device=dev)
-    capturing["on"] = False
-    assert s.get("out", 101, dtype=torch.float32, device=dev).numel() == 101
+def test_step_arena_is_carved_once_and_never_grows():
+    """The layer's buffers are regions of one allocation laid out at the token budget: a smaller
+    request is a slice at the same address, a larger one is refused (what the reference's
+    capture-safe scratch guarantees during graph capture, tests/python/test_vllm_experts.py:346-376,
+    holds here at all times)."""
+    arena = StepArena({"out": (torch.float32, 100), "ids": (torch.int32, 7), "act": (torch.bfloat16, 33)}, "cpu")
+    a = arena.take("out", 10)
+    b = arena.take("out", 100)
+    assert a.numel() == 10 and a.dtype == torch.float32 and b.data_ptr() == a.data_ptr()
+    assert arena.take("ids", 7).data_ptr() % 256 == arena.take("out", 1).data_ptr() % 256   # 256-byte pitch
+    assert arena.take("act", 33).data_ptr() >= arena.take("ids", 7).data_ptr() + 7 * 4
+    a.fill_(3.0)
+    arena.take("ids", 7).fill_(-1)
+    assert float(arena.take("out", 10).sum()) == 30.0                  # regions do not overlap
+    with pytest.raises(ValueError, match="token budget"):
+        arena.take("out", 101)
     with pytest.raises(ValueError):
-        s.get("out", -1, dtype=torch.float32, device=dev)
-
-
-def test_token_budget_hint(monkeypatch):
-    monkeypatch.delenv("MAX_NUM_BATCHED_TOKENS", raising=False)
-    monkeypatch.delenv("VLLM_MAX_NUM_BATCHED_TOKENS", raising=False)
-    assert max_num_tokens_hint() == 8192
-    monkeypatch.setenv("MAX_NUM_BATCHED_TOKENS", "512")
-    assert max_num_tokens_hint() == 512
+        arena.take("out", -1)
+    with pytest.raises(KeyError):
+        arena.take("nope", 1)
 
 
 def test_generator_is_reproducible_and_in_range():

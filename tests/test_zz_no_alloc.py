@@ -60,6 +60,32 @@ def test_noalloc_align_matches_regular_entry_point_twice():
         assert em0 == em1 and np.array_equal(s0, s1) and np.array_equal(e0, e1), (M, k, E, bs)
 
 
+def test_noalloc_align_at_its_limits_matches_the_oracle():
+    """The largest problem the fixed array holds - 262144 routed slots over 512 local experts, which
+    also takes the kernels' large shared-memory configuration - plus the same size through an
+    expert map and a call with no local expert at all, against the CPU oracle's alignment and the
+    regular entry point."""
+    import oracle
+
+    oracle.build()
+    rng = np.random.default_rng(12)
+    E, bs = 512, 16
+    M, k = 32768, 8                                   # M * k = 262144
+    ids_np = rng.integers(0, E, (M, k)).astype(np.int32)
+    ids = torch.from_numpy(ids_np).to(DEV)
+    for emap_np, local_n in [(None, 512), (np.where(np.arange(E) % 2 == 0, np.arange(E) // 2, -1).astype(np.int32), 256),
+                             (np.full(E, -1, np.int32), 0)]:
+        emap = None if emap_np is None else torch.from_numpy(emap_np).to(DEV)
+        max_EM = ops.align_em_bound(M, k, max(local_n, 1), bs)
+        rc1, s1, e1, em1 = _call("vk_cuda_moe_align_block_size_noalloc", ids, emap, E, local_n, bs, max_EM)
+        assert rc1 == 0, nr.last_error()
+        rc0, s0, e0, em0 = _call("vk_hip_moe_align_block_size", ids, emap, E, local_n, bs, max_EM)
+        assert rc0 == 0 and em0 == em1 and np.array_equal(s0, s1) and np.array_equal(e0, e1)
+        full_map = np.arange(E, dtype=np.int32) if emap_np is None else emap_np
+        rs, re, rEM = oracle.moe_align_block_size_map(ids_np, full_map, E, local_n, bs, max_EM)
+        assert em1 == rEM and np.array_equal(s1, rs) and np.array_equal(e1, re), local_n
+
+
 def test_noalloc_align_rejects_sizes_beyond_its_fixed_scratch():
     lib = nr.load_library()
     one = torch.zeros(16, dtype=torch.int32, device=DEV)

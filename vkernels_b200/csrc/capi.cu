@@ -18,7 +18,13 @@ int sm100_last_status();
 void timing_begin(int max_calls);
 void timing_end(float* gateup_ms, float* down_ms, int* calls);
 void launch_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out, int rows,
-                         int K, cudaStream_t stream);
+                         int K, int path, cudaStream_t stream);
+void sm100_reset_status();
+int ep_last_status();
+void ep_reset_status();
+void ep_launch_flag_barrier(const unsigned long long* flag_bases, int world, int rank, int slot, int epoch,
+                            long long limit_clocks, cudaStream_t stream);
+void launch_wait_timeout_probe(long long limit_clocks, cudaStream_t stream);
 void ep_launch_pack(const uint16_t* x, const int32_t* topk_ids, const float* topk_w, int T, int H,
                     int k, int n_shared, int world, int rank, const int32_t* expert_begin,
                     int32_t* cursor, int32_t* row_of, uint16_t* send_x, int32_t* send_ids,
@@ -183,8 +189,26 @@ size_t vk_cuda_moe_workspace_bytes(int max_EM, int hidden, int ispp, int n_local
 }
 int vk_cuda_moe_reserve_workspace(size_t bytes) {
   VK_TRY
-  vkc::reserve_workspace(bytes);
+  vkc::reserve_workspace(bytes, nullptr);
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+int vk_cuda_moe_reserve_workspace_on(size_t bytes, void* stream) {
+  VK_TRY
+  vkc::reserve_workspace(bytes, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+int vk_cuda_moe_release_workspaces(void) {
+  VK_TRY
+  vkc::release_workspaces();
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+size_t vk_cuda_moe_workspace_live_bytes(void) {
+  try {
+    return vkc::workspace_live_bytes();
+  } catch (const std::exception& e) {
+    set_error(VK_ERROR_INTERNAL, e.what());
+    return 0;
+  }
 }
 
 /* 0 = every tensor-core launch so far completed its waits; otherwise the code
@@ -193,9 +217,32 @@ int vk_cuda_moe_kernel_status(void) {
   VK_TRY
   const int s = vkc::sm100_last_status();
   if (s != 0) {
-    set_error(VK_ERROR_INTERNAL, "a tcgen05 MoE kernel gave up on a bounded wait");
+    const std::string m = "a tcgen05 MoE kernel gave up on a bounded wait (code " + std::to_string(s) + ")";
+    set_error(VK_ERROR_INTERNAL, m.c_str());
     return VK_ERROR_INTERNAL;
   }
+  const int e = vkc::ep_last_status();
+  if (e != 0) {
+    const std::string m = "a cross-rank flag barrier gave up on a bounded wait for rank " + std::to_string(e - 200);
+    set_error(VK_ERROR_INTERNAL, m.c_str());
+    return VK_ERROR_INTERNAL;
+  }
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+/* Clears the status word of the current device. Synchronises the device. */
+int vk_cuda_moe_reset_kernel_status(void) {
+  VK_TRY
+  vkc::sm100_reset_status();
+  vkc::ep_reset_status();
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+/* Test hook: one warp waits, with the kernels' own bounded wait, on a barrier nobody arrives on
+ * and gives up after limit_clocks SM clocks, which sets the status word. Nothing hangs. */
+int vk_cuda_moe_test_wait_timeout(long long limit_clocks, void* stream) {
+  VK_TRY
+  vkc::launch_wait_timeout_probe(limit_clocks, static_cast<cudaStream_t>(stream));
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 
@@ -215,17 +262,23 @@ int vk_cuda_moe_timing_end(float* gateup_ms, float* down_ms, int* calls) {
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 
-/* Test hook: out[rows, K] bf16 = dequantised packed[rows, K/2] with scale[rows, K/32],
- * through the same device function the GEMM kernels use. */
-int vk_cuda_mxfp4_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
-                               int rows, int K, void* stream) {
+/* Test hooks: out[rows, K] bf16 = dequantised packed[rows, K/2] with scale[rows, K/32], through
+ * the device functions the GEMM kernels decode with. vk_cuda_mxfp4_dequant_rows runs the
+ * byte-permute decoder of the CTA-pair form; the _path variant selects the decoder:
+ * 0 = byte permutes, 1 = the shared-memory table of the lone-CTA form (K % 64 == 0). */
+int vk_cuda_mxfp4_dequant_rows_path(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
+                                    int rows, int K, int path, void* stream) {
   VK_TRY
   vkc::expects(rows >= 0 && K > 0 && K % 32 == 0, "mxfp4_dequant_rows: K must be a multiple of 32");
   if (rows > 0) {
     vkc::expects(packed && scale && out, "mxfp4_dequant_rows: null buffer");
-    vkc::launch_dequant_rows(packed, scale, out, rows, K, static_cast<cudaStream_t>(stream));
+    vkc::launch_dequant_rows(packed, scale, out, rows, K, path, static_cast<cudaStream_t>(stream));
   }
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+int vk_cuda_mxfp4_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out,
+                               int rows, int K, void* stream) {
+  return vk_cuda_mxfp4_dequant_rows_path(packed, scale, out, rows, K, 0, stream);
 }
 
 /* ---------------- expert-parallel helpers (device pointers) ------------- */
@@ -295,6 +348,14 @@ int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_cou
                                   reinterpret_cast<unsigned long long*>(a_rows),
                                   reinterpret_cast<unsigned long long*>(out_rows),
                                   static_cast<cudaStream_t>(stream));
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_flag_barrier(const uint64_t* flag_bases, int world, int rank, int slot, int epoch,
+                                long long limit_clocks, void* stream) {
+  VK_TRY
+  vkc::ep_launch_flag_barrier(reinterpret_cast<const unsigned long long*>(flag_bases), world, rank, slot, epoch,
+                              limit_clocks, static_cast<cudaStream_t>(stream));
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 

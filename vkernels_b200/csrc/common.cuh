@@ -25,15 +25,17 @@ inline void expects(bool ok, const char* msg) {
   if (!ok) throw std::invalid_argument(msg);
 }
 
-// Grow-only device scratch owned by the library, one per device.
-struct Workspace {
-  void* ptr = nullptr;
-  size_t bytes = 0;
-};
-// Returns a pointer to at least `bytes` of device memory on the current
-// device. Grows (cudaMalloc, after a device-wide synchronise and cudaFree of
-// the old block) when the request exceeds what is held.
-void* workspace_get(size_t bytes);
+// Library-owned device scratch (tile lists, gathered activation rows, alignment histograms): one
+// block per (device, stream), so calls on different streams never share scratch. A block is
+// allocated on the first call of its stream, or ahead of time by reserve_workspace; when a later
+// call needs more, a larger block is allocated and the old one is kept until
+// release_workspaces() - work already enqueued, or a captured graph, may still point at it.
+// No call synchronises the device or frees memory. While `stream` is being captured nothing can
+// be allocated: the call throws std::invalid_argument (reserve before capturing).
+void* workspace_get(size_t bytes, cudaStream_t stream);
+
+// Number of SMs of the current device.
+int sm_count();
 
 // ---------------------------------------------------------------------------
 // MXFP4 decode (bit-exact against the layer's CPU definition)
@@ -88,6 +90,52 @@ __device__ __forceinline__ void dequant8(uint32_t w, uint32_t scale2, uint32_t o
   out[1] = mul_bf16x2(prmt(loA, hiA, 0x7362u), scale2);
   out[2] = mul_bf16x2(prmt(loB, hiB, 0x5140u), scale2);
   out[3] = mul_bf16x2(prmt(loB, hiB, 0x7362u), scale2);
+}
+
+// Expansion through a shared-memory table (256 entries of one bf16 pair, replicated once per
+// bank: lane l reads word 32 * byte + l, 32 KB in all): per byte of packed weights one
+// integer-pipe instruction to isolate it, one multiply-add for the address, one load and one
+// bf16x2 multiply - a quarter of the integer-pipe work of the permute-based dequant8. Same
+// bits: table value (exact) times scale in one bf16 multiply.
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// 64 nibbles (two 16-byte chunks, one scale each) in three passes over the same 32 registers:
+// all table addresses, all loads, all multiplies - every pass is 32 independent instructions,
+// so a lone warp keeps its pipes busy instead of walking one dependent chain at a time.
+__device__ __forceinline__ void dequant64_lut(const uint4& p0, const uint4& p1, uint32_t s0, uint32_t s1,
+                                              uint32_t lut_lane, uint32_t (&v)[32]) {
+  const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[4 * i + 0] = lut_lane + (w[i] & 0xFFu) * 128u;
+    v[4 * i + 1] = lut_lane + prmt(w[i], 0u, 0x4441u) * 128u;
+    v[4 * i + 2] = lut_lane + prmt(w[i], 0u, 0x4442u) * 128u;
+    v[4 * i + 3] = lut_lane + (w[i] >> 24) * 128u;
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = lds_u32(v[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = mul_bf16x2(v[i], s0);
+#pragma unroll
+  for (int i = 16; i < 32; ++i) v[i] = mul_bf16x2(v[i], s1);
+}
+// bf16 bit pattern of one nibble code (sign in bit 3) under the layer's table
+__device__ __forceinline__ uint32_t e2m1_bf16_bits(uint32_t code) {
+  const uint32_t m = code & 7u;
+  const uint32_t mag = m == 0 ? 0x0000u : m == 1 ? 0x3E80u : m == 2 ? 0x3F80u : m == 3 ? 0x3FC0u
+                     : m == 4 ? 0x4000u : m == 5 ? 0x4040u : m == 6 ? 0x7F80u : 0x7FC0u;
+  return mag | ((code & 8u) << 12);
+}
+
+// Fills the replicated table used by dequant64_lut (all threads of the CTA take part).
+__device__ __forceinline__ void fill_dequant_lut(uint32_t* lut, int tid, int n_threads) {
+  for (int i = tid; i < 256 * 32; i += n_threads) {
+    const uint32_t byte = (uint32_t)i >> 5;
+    lut[i] = e2m1_bf16_bits(byte & 15u) | (e2m1_bf16_bits(byte >> 4) << 16);
+  }
 }
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) { return __uint_as_float(b16 << 16); }

@@ -12,6 +12,8 @@
 // Large N runs three kernels over 1024-entry chunks: per-chunk histograms,
 // a scan over (expert, chunk), and an ordered scatter; the chunk histograms
 // live in the library workspace.
+#include <atomic>
+
 #include "common.cuh"
 #include "moe_fused.hpp"
 
@@ -215,10 +217,10 @@ void moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map, in
                                                local_n, max_EM, sorted_ids, expert_ids, out_em);
   } else {
     const int n_chunks = (N + kChunk - 1) / kChunk;
-    // The first 4 KB of the workspace hold the tile count and the status word of the GEMM
-    // kernels, which must survive from call to call: the histograms start behind them.
+    // The histograms use this stream's workspace block behind its first 4 KB (the tile count of
+    // the GEMM kernels); they are dead before the same stream builds the tile list.
     int* ws = reinterpret_cast<int*>(
-        static_cast<uint8_t*>(workspace_get(4096 + ((size_t)n_chunks * ln + ln) * sizeof(int))) + 4096);
+        static_cast<uint8_t*>(workspace_get(4096 + ((size_t)n_chunks * ln + ln) * sizeof(int), s)) + 4096);
     int* hist = ws;
     int* offset = ws + (size_t)n_chunks * ln;
     if (hist_smem > 48 * 1024) {
@@ -297,16 +299,15 @@ void moe_align_block_size_noalloc(const int32_t* topk_ids, const int32_t* expert
   const int n_chunks = N > 0 ? (N + kChunk - 1) / kChunk : 1;
 
   // Device address of the array, looked up once per device with that device current.
-  static int* scratch_of_device[64] = {};
+  static std::atomic<int*> scratch_of_device[64];
   int dev = 0;
   VK_CUDA_CHECK(cudaGetDevice(&dev));
   expects(dev >= 0 && dev < 64, "moe_align_block_size_noalloc: device index out of range");
-  if (scratch_of_device[dev] == nullptr) {
-    int* ptr = nullptr;
-    VK_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_align_scratch));
-    scratch_of_device[dev] = ptr;
+  int* hist = scratch_of_device[dev].load();
+  if (hist == nullptr) {
+    VK_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&hist), g_noalloc_align_scratch));
+    scratch_of_device[dev].store(hist);   // two threads racing here store the same address
   }
-  int* hist = scratch_of_device[dev];
   int* offset = hist + (size_t)n_chunks * ln;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);

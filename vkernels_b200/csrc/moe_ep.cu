@@ -241,6 +241,41 @@ ep_unpack_meta_peer_kernel(const int32_t* __restrict__ meta, const int32_t* __re
   }
 }
 
+// ---------------------------------------------------------------------------
+// Cross-rank barrier on flags in peer-visible memory, with bounded waits
+// ---------------------------------------------------------------------------
+// Every rank owns a flag array [slots][world] of int32 that all ranks can address. Thread d of
+// the single CTA first publishes this rank's arrival - `epoch` stored with system-scope release
+// into entry [slot][rank] of rank d's array, after a system-scope fence that orders every
+// earlier write of this stream (peer stores included) before it - and then waits, with a
+// system-scope acquire load, until entry [slot][d] of its OWN array has reached `epoch`.
+// Epochs only grow, so nothing is ever reset. The wait is limited to `limit_clocks` SM clocks:
+// a rank that never arrives makes the others record a status (200 + the missing rank) and
+// return instead of spinning, and the host reads that status before trusting the step.
+__device__ int g_ep_status;
+
+__global__ void __launch_bounds__(32)
+ep_flag_barrier_kernel(const unsigned long long* __restrict__ flag_bases, int world, int rank, int slot,
+                       int epoch, long long limit_clocks) {
+  const int d = threadIdx.x;
+  if (d >= world) return;
+  __threadfence_system();
+  int* theirs = reinterpret_cast<int*>(flag_bases[d]) + slot * world + rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+  const int* mine = reinterpret_cast<const int*>(flag_bases[rank]) + slot * world + d;
+  const long long t0 = clock64();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v - epoch >= 0) break;
+    if (clock64() - t0 > limit_clocks) {
+      atomicExch(&g_ep_status, 200 + d);
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+
 // out[r, k] = dequantised weight (bf16 bits); one thread per 8 elements.
 __global__ void __launch_bounds__(256)
 dequant_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
@@ -255,6 +290,29 @@ dequant_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
   dequant8(word, ue8m0_to_bf16x2(s), o);
   uint4* dst = reinterpret_cast<uint4*>(out + r * K + wq * 8);
   *dst = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// The same rows through the table expansion of the lone-CTA GEMM form: one thread per 64
+// K-elements (two 16-byte chunks, one scale each), table built per CTA exactly as the GEMM does.
+__global__ void __launch_bounds__(256)
+dequant_rows_lut_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
+                        uint16_t* __restrict__ out, int rows, int K) {
+  __shared__ uint32_t lut[256 * 32];
+  fill_dequant_lut(lut, threadIdx.x, blockDim.x);
+  __syncthreads();
+  const size_t pieces_per_row = K / 64;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * pieces_per_row) return;
+  const size_t r = i / pieces_per_row, pc = i % pieces_per_row;
+  const uint4* src = reinterpret_cast<const uint4*>(packed + r * (K / 2) + pc * 32);
+  const uint32_t s0 = ue8m0_to_bf16x2(scale[r * (K / 32) + pc * 2]);
+  const uint32_t s1 = ue8m0_to_bf16x2(scale[r * (K / 32) + pc * 2 + 1]);
+  uint32_t v[32];
+  const uint32_t lut_lane = static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (threadIdx.x & 31u) * 4u;
+  dequant64_lut(src[0], src[1], s0, s1, lut_lane, v);
+  uint4* dst = reinterpret_cast<uint4*>(out + r * K + pc * 64);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dst[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
 }
 
 }  // namespace
@@ -333,6 +391,28 @@ void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts,
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
+void ep_launch_flag_barrier(const unsigned long long* flag_bases, int world, int rank, int slot, int epoch,
+                            long long limit_clocks, cudaStream_t stream) {
+  expects(world >= 1 && world <= 32 && rank >= 0 && rank < world, "ep_flag_barrier: bad world/rank");
+  expects(slot >= 0 && slot < 8 && flag_bases != nullptr, "ep_flag_barrier: bad slot or null flag table");
+  expects(limit_clocks > 0 && limit_clocks <= 8000000000ll, "ep_flag_barrier: limit must be in (0, 8e9] clocks");
+  ep_flag_barrier_kernel<<<1, 32, 0, stream>>>(flag_bases, world, rank, slot, epoch, limit_clocks);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+// 0, or 200 + the rank whose arrival a flag barrier gave up waiting for. Synchronises the device.
+int ep_last_status() {
+  int v = 0;
+  VK_CUDA_CHECK(cudaDeviceSynchronize());
+  VK_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_ep_status, sizeof(int)));
+  return v;
+}
+void ep_reset_status() {
+  const int zero = 0;
+  VK_CUDA_CHECK(cudaDeviceSynchronize());
+  VK_CUDA_CHECK(cudaMemcpyToSymbol(g_ep_status, &zero, sizeof(int)));
+}
+
 void ep_launch_combine(const float* rows, const int32_t* row_of, int T, int H, int world,
                        uint16_t* out_bf16, float* out_f32, cudaStream_t stream) {
   expects(T >= 0 && H > 0 && H % 4 == 0 && world >= 1, "ep_combine: bad dimensions");
@@ -342,10 +422,20 @@ void ep_launch_combine(const float* rows, const int32_t* row_of, int T, int H, i
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
+// path 0: the byte-permute decoder (CTA-pair GEMM form); path 1: the table decoder (lone-CTA form).
 void launch_dequant_rows(const uint8_t* packed, const uint8_t* scale, uint16_t* out, int rows,
-                         int K, cudaStream_t stream) {
-  const size_t n = (size_t)rows * (K / 8);
-  dequant_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(packed, scale, out, rows, K);
+                         int K, int path, cudaStream_t stream) {
+  expects(path == 0 || path == 1, "mxfp4_dequant_rows: path must be 0 (permute) or 1 (table)");
+  if (path == 0) {
+    const size_t n = (size_t)rows * (K / 8);
+    dequant_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(packed, scale, out, rows, K);
+  } else {
+    expects(K % 64 == 0, "mxfp4_dequant_rows: the table path takes K in multiples of 64");
+    expects((reinterpret_cast<uintptr_t>(packed) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0,
+            "mxfp4_dequant_rows: the table path needs 16-byte aligned buffers");
+    const size_t n = (size_t)rows * (K / 64);
+    dequant_rows_lut_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(packed, scale, out, rows, K);
+  }
   VK_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -49,36 +50,90 @@ MoeImpl get_moe_impl() {
 }
 
 // ---------------------------------------------------------------------------
-// workspace: one grow-only block per device
+// workspace: one block per (device, stream); see common.cuh for the rules
 // ---------------------------------------------------------------------------
 namespace {
 constexpr int kMaxDevices = 64;
-Workspace g_ws[kMaxDevices];
+struct WsBlock {
+  int dev;
+  cudaStream_t stream;
+  void* ptr;
+  size_t bytes;
+};
+std::vector<WsBlock> g_ws_live;      // at most one per (device, stream)
+std::vector<WsBlock> g_ws_retired;   // outgrown blocks, kept for work that may still use them
 std::mutex g_ws_mutex;
+std::atomic<int> g_sm_count[kMaxDevices];
 }  // namespace
 
-void* workspace_get(size_t bytes) {
+int sm_count() {
   int dev = 0;
   VK_CUDA_CHECK(cudaGetDevice(&dev));
-  expects(dev >= 0 && dev < kMaxDevices, "workspace: device index out of range");
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
-  Workspace& ws = g_ws[dev];
-  if (ws.bytes < bytes) {
-    // Work already enqueued may still read the old block.
-    VK_CUDA_CHECK(cudaDeviceSynchronize());
-    if (ws.ptr != nullptr) VK_CUDA_CHECK(cudaFree(ws.ptr));
-    ws.ptr = nullptr;
-    ws.bytes = 0;
-    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    VK_CUDA_CHECK(cudaMalloc(&ws.ptr, want));
-    // the first 4 KB hold counters and the status word of the GEMM kernels
-    VK_CUDA_CHECK(cudaMemset(ws.ptr, 0, 4096));
-    ws.bytes = want;
+  const bool known = dev >= 0 && dev < kMaxDevices;
+  int v = known ? g_sm_count[dev].load() : 0;
+  if (v == 0) {
+    VK_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+    if (known) g_sm_count[dev].store(v);
   }
-  return ws.ptr;
+  return v;
 }
 
-void reserve_workspace(size_t bytes) { (void)workspace_get(bytes); }
+void* workspace_get(size_t bytes, cudaStream_t stream) {
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  WsBlock* mine = nullptr;
+  for (auto& b : g_ws_live)
+    if (b.dev == dev && b.stream == stream) mine = &b;
+  if (mine != nullptr && mine->bytes >= bytes) return mine->ptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  VK_CUDA_CHECK(cudaStreamIsCapturing(stream, &cap));
+  expects(cap == cudaStreamCaptureStatusNone,
+          "fused_moe_mxfp4: the workspace of this stream is too small and the stream is being "
+          "captured; call vk_cuda_moe_reserve_workspace_on(bytes, stream) before the capture");
+  const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  void* p = nullptr;
+  VK_CUDA_CHECK(cudaMalloc(&p, want));
+  if (mine != nullptr) {
+    g_ws_retired.push_back(*mine);
+    mine->ptr = p;
+    mine->bytes = want;
+  } else {
+    g_ws_live.push_back(WsBlock{dev, stream, p, want});
+  }
+  return p;
+}
+
+void reserve_workspace(size_t bytes, void* stream) { (void)workspace_get(bytes, static_cast<cudaStream_t>(stream)); }
+
+// Frees every block of the current device, live and retired. The caller guarantees that no work
+// using them is pending and that no captured graph that points at them will be replayed.
+void release_workspaces() {
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  for (auto* v : {&g_ws_live, &g_ws_retired}) {
+    for (size_t i = 0; i < v->size();) {
+      if ((*v)[i].dev == dev) {
+        VK_CUDA_CHECK(cudaFree((*v)[i].ptr));
+        v->erase(v->begin() + (long)i);
+      } else {
+        ++i;
+      }
+    }
+  }
+}
+
+size_t workspace_live_bytes() {
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  size_t n = 0;
+  for (auto* v : {&g_ws_live, &g_ws_retired})
+    for (auto& b : *v)
+      if (b.dev == dev) n += b.bytes;
+  return n;
+}
 
 size_t workspace_bytes_required(int max_EM, int hidden, int ispp, int n_local_experts, int N) {
   const size_t align_bytes =

@@ -130,14 +130,18 @@ void route_topk(const float* logits, const float* bias, int T, int E, int k, int
                 int n_group, int topk_group, int renorm, float scaling, int n_shared,
                 int32_t* ids, float* w, void* stream);
 
-// Library-owned device scratch (tile lists, alignment histograms, the gathered
-// activation rows of the gate/up GEMM). It is sized on first use and grown
-// when a larger problem arrives; growth calls cudaMalloc and therefore must
-// not happen during stream capture: call reserve_workspace once, before
-// capture, with the largest problem.
+// Library-owned device scratch (tile lists, the gathered activation rows of the gate/up GEMM,
+// alignment histograms): one block per (device, stream), so layer calls on different streams do
+// not share scratch; calls on ONE stream are ordered by the stream and reuse its block. A block
+// is allocated by the first call on its stream or by reserve_workspace; a call that needs more
+// allocates a larger block and keeps the old one until release_workspaces (enqueued work or a
+// captured graph may still use it). No launcher synchronises or frees. During stream capture an
+// allocation is impossible and the call fails with std::invalid_argument: reserve first.
 size_t workspace_bytes_required(int max_EM, int hidden, int ispp, int n_local_experts,
                                 int N);
-void reserve_workspace(size_t bytes);
+void reserve_workspace(size_t bytes, void* stream = nullptr);
+void release_workspaces();
+size_t workspace_live_bytes();
 
 }  // namespace cuda
 }  // namespace vkernels::kernels

@@ -92,6 +92,11 @@ constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x
 constexpr int kLutBytes = 256 * 32 * 4;
 constexpr long long kWaitLimitClocks = 4000000000ll;   // about two seconds of SM clock
 
+// Device status word of the tensor-core kernels: 0, or 100 + the code of the wait that ran out.
+// It lives in the library image (one per GPU that loads the library), so no launch needs a
+// buffer for it and nothing but an expired wait writes it.
+__device__ int g_kernel_status;
+
 struct TokTile {
   int expert;
   int row0;
@@ -112,7 +117,6 @@ struct GemmParams {
   int k_base;                 // first column of the token rows this launch reduces over (K-sharded weights)
   const TokTile* tiles;
   const int* n_tiles;
-  int* status;                // device status word (0 = ok)
   int K;                      // reduction length (hidden for gate/up, ispp for down)
   int n_feat;                 // gate/up: ispp; down: hidden
   int n_ftiles;
@@ -168,7 +172,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // for a whole item's MMAs, a producer waiting for a free slot of a deep ring): the warp sleeps
 // between polls instead of spending issue slots that the dequant warps of the same scheduler need.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code, unsigned sleep_ns = 0) {
+                                          int code, unsigned sleep_ns = 0,
+                                          long long limit_clocks = kWaitLimitClocks) {
   // try_wait suspends the thread for a hardware-chosen slice, so the limit is kept in clock
   // cycles rather than in poll iterations.
   long long t0 = 0;
@@ -179,7 +184,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitClocks) {
+      if (now - t0 > limit_clocks) {
         *abort_flag = code;
         return false;
       }
@@ -340,6 +345,28 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+// The same reduction at system scope, for output rows that may live in another GPU's memory:
+// several GPUs add into one row, and only system-scope atomics from different GPUs on one
+// address are ordered with respect to each other by the memory model.
+__device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+// Named barrier that also ORs a predicate over its participants.
+__device__ __forceinline__ bool named_bar_or(int id, int n, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 q, %1, 0;\n"
+      "barrier.cta.red.or.pred p, %2, %3, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "r"(id), "r"(n)
+      : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -403,43 +430,6 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
-// Expansion through the shared-memory table (see kLutBytes): per byte of packed weights one
-// integer-pipe instruction to isolate it, one multiply-add for the address, one load and one
-// bf16x2 multiply - a quarter of the integer-pipe work of the permute-based dequant8. Same
-// bits: table value (exact) times scale in one bf16 multiply.
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-// 64 nibbles (two 16-byte chunks, one scale each) in three passes over the same 32 registers:
-// all table addresses, all loads, all multiplies - every pass is 32 independent instructions,
-// so a lone warp keeps its pipes busy instead of walking one dependent chain at a time.
-__device__ __forceinline__ void dequant64_lut(const uint4& p0, const uint4& p1, uint32_t s0, uint32_t s1,
-                                              uint32_t lut_lane, uint32_t (&v)[32]) {
-  const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[4 * i + 0] = lut_lane + (w[i] & 0xFFu) * 128u;
-    v[4 * i + 1] = lut_lane + prmt(w[i], 0u, 0x4441u) * 128u;
-    v[4 * i + 2] = lut_lane + prmt(w[i], 0u, 0x4442u) * 128u;
-    v[4 * i + 3] = lut_lane + (w[i] >> 24) * 128u;
-  }
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = lds_u32(v[i]);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = mul_bf16x2(v[i], s0);
-#pragma unroll
-  for (int i = 16; i < 32; ++i) v[i] = mul_bf16x2(v[i], s1);
-}
-// bf16 bit pattern of one nibble code (sign in bit 3) under the layer's table
-__device__ __forceinline__ uint32_t e2m1_bf16_bits(uint32_t code) {
-  const uint32_t m = code & 7u;
-  const uint32_t mag = m == 0 ? 0x0000u : m == 1 ? 0x3E80u : m == 2 ? 0x3F80u : m == 3 ? 0x3FC0u
-                     : m == 4 ? 0x4000u : m == 5 ? 0x4040u : m == 6 ? 0x7F80u : 0x7FC0u;
-  return mag | ((code & 8u) << 12);
-}
-
 __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
@@ -529,12 +519,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
-  if (kUseLut) {
-    for (int i = tid; i < 256 * 32; i += kThreads) {
-      const uint32_t byte = (uint32_t)i >> 5;
-      lut[i] = e2m1_bf16_bits(byte & 15u) | (e2m1_bf16_bits(byte >> 4) << 16);
-    }
-  }
+  if (kUseLut) fill_dequant_lut(lut, tid, kThreads);
   if (tid == 0) {
     for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
@@ -951,8 +936,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         if (!GATEUP) bars->tile_w[j] = (real && p.topk_w != nullptr) ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
       }
-      named_bar_sync(1, 128 * kEpiSets);
-      if (!mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256)) break;
+      // The wait's outcome is shared by all epilogue warps before anyone acts on it: a warp that
+      // gave up must not leave the others standing at a later named barrier.
+      const bool gave_up = !mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256);
+      if (named_bar_or(1, 128 * kEpiSets, gave_up)) break;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       auto release_acc = [&]() {
@@ -1079,8 +1066,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 if (orow != nullptr && quad_ok) {
                   const float wgt = bars->tile_w[t];
                   const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
-                  red_add_v4(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
-                             (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
+                  if (p.out_rows != nullptr)
+                    red_add_v4_sys(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
+                                   (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
+                  else
+                    red_add_v4(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
+                               (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
                 }
               }
             }
@@ -1122,7 +1113,25 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    "r"((uint32_t)kTmemCols)
                    : "memory");
   }
-  if (tid == 0 && bars->abort_flag != 0) atomicExch(p.status, 100 + bars->abort_flag);
+  if (tid == 0 && bars->abort_flag != 0) atomicExch(&g_kernel_status, 100 + bars->abort_flag);
+}
+
+// One warp waits, with the kernels' own bounded wait, on a barrier nobody arrives on, and
+// reports the expiry through the status word like a GEMM kernel would: the way to exercise the
+// give-up path without starving a real launch.
+__global__ void wait_timeout_probe_kernel(long long limit_clocks) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, 99, 0, limit_clocks);
+    if (!ok) atomicExch(&g_kernel_status, 100 + abort_flag);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1267,13 +1276,12 @@ CUtensorMap make_map(const void* ptr, CUtensorMapDataType dt, int elem_bytes, ui
 int max_tok_tiles(int EM) { return EM / 16 + 1; }
 
 struct WsLayout {
-  size_t tiles_off, count_off, status_off, gathered_off, total;
+  size_t tiles_off, count_off, gathered_off, total;
 };
 WsLayout ws_layout(int EM, int hidden) {
   WsLayout l{};
   size_t off = 0;
   l.count_off = off;  off += 256;
-  l.status_off = l.count_off + 64;
   l.tiles_off = off;  off += (size_t)max_tok_tiles(EM) * sizeof(TokTile);
   off = (off + 1023) & ~size_t(1023);
   l.gathered_off = off;  off += (size_t)EM * hidden * sizeof(uint16_t);
@@ -1281,15 +1289,6 @@ WsLayout ws_layout(int EM, int hidden) {
   return l;
 }
 
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    VK_CUDA_CHECK(cudaGetDevice(&dev));
-    VK_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-    return v;
-  }();
-  return n;
-}
 
 // Large token tiles run on CTA pairs; VK_MOE_PAIR=0 keeps every launch on single CTAs.
 bool pair_mode() {
@@ -1443,14 +1442,27 @@ void timer_mark(int which, cudaStream_t stream) {
 }  // namespace
 
 
-// Status of the most recent tcgen05 launches on the current device: 0, or
+// Status of the tcgen05 launches on the current device since the last reset: 0, or
 // 100 + the code of the wait that ran out. Synchronises the device.
 int sm100_last_status() {
   int v = 0;
-  uint8_t* ws = static_cast<uint8_t*>(workspace_get(4096));
   VK_CUDA_CHECK(cudaDeviceSynchronize());
-  VK_CUDA_CHECK(cudaMemcpy(&v, ws + 64, sizeof(int), cudaMemcpyDeviceToHost));
+  VK_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof(int)));
   return v;
+}
+
+// Clears the status word of the current device (after the failure has been dealt with).
+void sm100_reset_status() {
+  const int zero = 0;
+  VK_CUDA_CHECK(cudaDeviceSynchronize());
+  VK_CUDA_CHECK(cudaMemcpyToSymbol(g_kernel_status, &zero, sizeof(int)));
+}
+
+// Launches the one-warp probe whose bounded wait is certain to run out after `limit_clocks`.
+void launch_wait_timeout_probe(long long limit_clocks, cudaStream_t stream) {
+  expects(limit_clocks > 0 && limit_clocks <= 2000000000ll, "wait probe: limit must be in (0, 2e9] clocks");
+  wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(limit_clocks);
+  VK_CUDA_CHECK(cudaGetLastError());
 }
 
 
@@ -1504,10 +1516,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
               aligned16(w2_scale) && aligned16(act_scratch),
           "fused_moe_mxfp4: A, weights, scales and act_scratch must be 16-byte aligned");
   const WsLayout l = ws_layout(EM, hidden);
-  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total));
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total, stream));
   TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
   int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);
-  int* status = reinterpret_cast<int*>(ws + l.status_off);
   uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
 
   // The number of experts is not an argument of the layer; the tensor maps
@@ -1522,7 +1533,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                                                        M * top_k, top_k, hidden, gathered);
 
   GemmParams g{};
-  g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles; g.status = status;
+  g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles;
   g.N = M * top_k; g.top_k = top_k; g.w_sorted = w_sorted; g.activation = activation;
   g.limit = swiglu_limit; g.beta = beta; g.linear_beta = linear_beta; g.max_tok = max_tok;
 
@@ -1579,10 +1590,9 @@ void launch_moe_stage_gemm(int which, const uint16_t* rows_in, const uint8_t* w,
   expects(aligned16(rows_in) && aligned16(w) && aligned16(w_scale) && aligned16(raw),
           "moe stage: buffers must be 16-byte aligned");
   const WsLayout l = ws_layout(EM, which == 0 ? k_full : 64);
-  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total));
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total, stream));
   TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
   int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);
-  int* status = reinterpret_cast<int*>(ws + l.status_off);
   uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
   const TileChoice choice = choose_tiles(M, top_k, EM, block_size, k_shard, k_shard);
   build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, choice.max_tok, tiles,
@@ -1594,7 +1604,7 @@ void launch_moe_stage_gemm(int which, const uint16_t* rows_in, const uint8_t* w,
     token_rows = gathered;
   }
   GemmParams p{};
-  p.sorted_ids = sorted_ids; p.tiles = tiles; p.n_tiles = n_tiles; p.status = status;
+  p.sorted_ids = sorted_ids; p.tiles = tiles; p.n_tiles = n_tiles;
   p.N = M * top_k; p.top_k = top_k; p.max_tok = choice.max_tok;
   p.w_scale = w_scale; p.K = k_shard; p.k_base = k_base; p.raw = raw;
   p.n_feat = n_out;

@@ -427,12 +427,12 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
   expects(T >= 0 && H > 0 && E > 0, "router_logits: bad dimensions");
   if (T == 0) return;
   expects(x && wr && logits, "router_logits: null buffer");
-  if (T <= 512 && H % 4 == 0) {
+  const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15u) == 0;
+  if (T <= 512 && H % 8 == 0 && aligned16) {   // 8- and 16-byte loads of whole rows
     const long long pairs = (long long)T * E;
     router_logits_warp_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, wr, logits, T, H, E);
-  } else if (H % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
-             (reinterpret_cast<uintptr_t>(wr) & 15u) == 0) {
+  } else if (H % 8 == 0 && aligned16) {
     // the attribute belongs to the device's context: once per device
     static std::atomic<bool> configured_dev[64];
     int dev = 0;
@@ -446,13 +446,13 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
       if (known) configured_dev[dev].store(true);
     }
     const int t_tiles = (T + MT - 1) / MT;
-    if (t_tiles * ((E + 127) / 128) >= 2 * 148) {
+    if (t_tiles * ((E + 127) / 128) >= 2 * sm_count()) {
       dim3 grid(t_tiles, (E + 127) / 128);
       router_logits_mma_kernel<128><<<grid, 256, sizeof(RouterSmem<128>), static_cast<cudaStream_t>(stream)>>>(
           x, wr, logits, T, H, E);
     } else {
       dim3 grid(t_tiles, (E + 63) / 64);
-      if ((int)(grid.x * grid.y) < 148 && H >= 4 * MK) {   // not enough CTAs for the machine: split K in two
+      if ((int)(grid.x * grid.y) < sm_count() && H >= 4 * MK) {   // not enough CTAs for the machine: split K in two
         grid.z = 2;
         VK_CUDA_CHECK(cudaMemsetAsync(logits, 0, (size_t)T * E * sizeof(float), static_cast<cudaStream_t>(stream)));
       }

@@ -144,8 +144,8 @@ class CudaBackend:
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def route(self, x):
-        return self.layer.route(x)
+    def route(self, x, logits=None):
+        return self.layer.route(x, logits=logits)
 
     def pack(self, x, ids, w, n_shared, world, rank, begins, cursor, row_of, send_x, send_ids, send_w, phase):
         T, H = x.shape
@@ -184,6 +184,12 @@ class CudaBackend:
                 self._stream())
         nr.check(rc, "ep_pack_meta_peer")
 
+    def flag_barrier(self, flag_bases, world, rank, slot, epoch, limit_clocks):
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_flag_barrier(flag_bases.data_ptr(), world, rank, slot, epoch,
+                                                               limit_clocks, self._stream())
+        nr.check(rc, "ep_flag_barrier")
+
     def unpack_meta_peer(self, meta, recv_counts, world, cap, slots, x_bases, out_bases, H, ids, w, a_rows,
                          out_rows):
         with torch.cuda.device(self.device):
@@ -221,6 +227,7 @@ class ExpertParallelMoE:
         self.count_local_slots = False   # last_stats()["local_slots"]: one extra host read per step
         self.time_phases = False         # last_stats()["phase_ms"]: CUDA events between the phases
         self._peer = None                # symmetric buffers of the peer-memory form
+        self._last_routing = None        # (ids, w) of the most recent call (views of layer buffers)
 
     @classmethod
     def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
@@ -264,15 +271,19 @@ class ExpertParallelMoE:
             stride = 1 + 2 * self.slots
             meta_sym = symm.empty((self.world * max_tokens, stride), dtype=torch.int32, device=self.device)
             cnt_sym = symm.empty((32,), dtype=torch.int32, device=self.device)
+            flag_sym = symm.empty((8 * 32,), dtype=torch.int32, device=self.device)
+            flag_sym.zero_()
             hx = symm.rendezvous(x_sym, group)
             ho = symm.rendezvous(out_sym, group)
             hm = symm.rendezvous(meta_sym, group)
             hc = symm.rendezvous(cnt_sym, group)
+            hf = symm.rendezvous(flag_sym, group)
             dev_ptrs = lambda h: torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=self.device)
             n_rows = self.world * max_tokens
             peer = {"x": x_sym, "out": out_sym, "meta": meta_sym, "cnt": cnt_sym, "hx": hx, "ho": ho,
                     "x_bases": dev_ptrs(hx), "out_bases": dev_ptrs(ho), "meta_bases": dev_ptrs(hm),
-                    "cnt_bases": dev_ptrs(hc), "max_tokens": max_tokens,
+                    "cnt_bases": dev_ptrs(hc), "flags": flag_sym, "flag_bases": dev_ptrs(hf), "epoch": 0,
+                    "max_tokens": max_tokens,
                     # routing arrays and row addresses of the expert call, one per record slot
                     "ids": torch.empty((n_rows, self.slots), dtype=torch.int32, device=self.device),
                     "w": torch.empty((n_rows, self.slots), dtype=torch.float32, device=self.device),
@@ -282,6 +293,7 @@ class ExpertParallelMoE:
         except Exception as e:  # noqa: BLE001 - any failure means "not available here"
             ok, err = 0, f"{type(e).__name__}: {e}"
         flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        # also orders every rank's zeroed flag array before anyone's first flag barrier
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         if int(flag.item()) == 1:
             self._peer = peer
@@ -290,7 +302,20 @@ class ExpertParallelMoE:
         self._stats["peer_memory_error"] = err
         return False
 
-    def _forward_peer(self, x: torch.Tensor, topk=None) -> torch.Tensor:
+    # A cross-rank wait must end by itself when a rank has left: about four seconds of SM clock,
+    # after which the status word reports the missing rank (``torch_ops.kernel_status``).
+    BARRIER_LIMIT_CLOCKS = 8_000_000_000
+
+    def _barrier(self, slot: int) -> None:
+        """Flag barrier over the ranks of the peer-memory form, as a kernel on the current stream
+        (bounded wait; see ``vk_cuda_moe_ep_flag_barrier``). Both slots advance once per step."""
+        peer = self._peer
+        if slot == 0:
+            peer["epoch"] += 1
+        self.backend.flag_barrier(peer["flag_bases"], self.world, self.rank, slot, peer["epoch"],
+                                  self.BARRIER_LIMIT_CLOCKS)
+
+    def _forward_peer(self, x: torch.Tensor, topk=None, logits=None) -> torch.Tensor:
         T, H = x.shape
         world, rank, slots = self.world, self.rank, self.slots
         dev = x.device
@@ -305,10 +330,11 @@ class ExpertParallelMoE:
 
         mark("start")
         if topk is None:
-            ids, w = self.backend.route(x)
+            ids, w = self.backend.route(x, logits=logits) if logits is not None else self.backend.route(x)
             ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
         else:
             ids, w = topk
+        self._last_routing = (ids, w)
         mark("route")
         # this rank's tokens and a zeroed output, where every rank can reach them
         x_sym, out_sym = peer["x"][:T], peer["out"][:T]
@@ -322,7 +348,7 @@ class ExpertParallelMoE:
                                     peer["cnt_bases"], cap)
         mark("records")
         # every rank's tokens, records and counts are in place and its output rows are zero
-        peer["hx"].barrier(channel=0)
+        self._barrier(0)
         mark("barrier_in")
         r_ids, r_w, a_rows, out_rows = peer["ids"], peer["w"], peer["a_rows"], peer["out_rows"]
         self.backend.unpack_meta_peer(peer["meta"], peer["cnt"], world, cap, slots, peer["x_bases"],
@@ -334,7 +360,7 @@ class ExpertParallelMoE:
             R_send, R_recv = int(cursor.sum()), int(peer["cnt"][:world].sum())
             local_slots = int((r_ids >= 0).sum())
         # every rank's additions into this rank's output rows are done
-        peer["ho"].barrier(channel=0)
+        self._barrier(1)
         mark("barrier_out")
         out = torch.empty((T, H), dtype=x.dtype, device=dev)
         out.copy_(out_sym)
@@ -353,11 +379,17 @@ class ExpertParallelMoE:
                        "local_slots": local_slots, "phase_ms": phase_ms}
         return out
 
-    def forward(self, x: torch.Tensor, topk=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk=None, logits=None) -> torch.Tensor:
         """x [T_local, H] bf16 -> bf16 [T_local, H]. `topk` = (ids [T, k] int32 GLOBAL expert ids,
-        weights [T, k] fp32) skips the router."""
-        if self._peer is not None and x.shape[0] <= self._peer["max_tokens"]:
-            return self._forward_peer(x, topk)
+        weights [T, k] fp32) skips the router; `logits` [T_local, E] fp32 replaces the router GEMM."""
+        if self._peer is not None:
+            # Every rank must take the same form (one waits at flags, the other inside a NCCL
+            # all-to-all otherwise), so a batch beyond the registered buffers is an error here
+            # rather than a silent switch of form on this rank alone.
+            if x.shape[0] > self._peer["max_tokens"]:
+                raise ValueError(f"peer-memory form was set up for {self._peer['max_tokens']} tokens per rank, "
+                                 f"got {x.shape[0]}; call enable_peer_memory with a larger budget on every rank")
+            return self._forward_peer(x, topk, logits)
         T, H = x.shape
         world, rank, slots = self.world, self.rank, self.slots
         dev = x.device
@@ -371,10 +403,11 @@ class ExpertParallelMoE:
 
         mark("start")
         if topk is None:
-            ids, w = self.backend.route(x)
+            ids, w = self.backend.route(x, logits=logits) if logits is not None else self.backend.route(x)
             ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
         else:
             ids, w = topk
+        self._last_routing = (ids, w)
         mark("route")
         # 2. counts
         counts = torch.zeros(world, dtype=torch.int32, device=dev)

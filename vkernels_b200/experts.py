@@ -1,13 +1,17 @@
-"""Layer object for the fused MXFP4 MoE: weights resident in HBM, persistent
-scratch sized once, the serving call sequence of the reference binding.
+"""Layer object for the fused MXFP4 MoE: weights resident in HBM, every buffer of a step carved
+out of ONE device allocation made when the layer is built, the serving call sequence of the
+reference binding (src/python/vkernels/vllm_experts.py:813-1092).
 
-``CaptureSafeScratch`` restates the reference's persistent-scratch manager
-(src/python/vkernels/vllm_experts.py:142-246): buffers are sized once at the
-token budget, later calls slice them, and growing is refused while a CUDA graph
-is being captured because the captured graph still points at the old storage.
+Scratch policy. The reference keeps persistent scratch tensors that are sized at a token budget
+and refuses to grow them while a CUDA graph is being captured
+(src/python/vkernels/vllm_experts.py:142-246). Here the question of growth does not arise: the
+layer takes its token budget as a constructor argument, lays all per-step buffers out in a single
+arena at that budget, and a batch beyond the budget is rejected whether or not a capture is
+active. Addresses therefore never change after construction, which is what graph replay needs.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 
 import torch
@@ -15,56 +19,58 @@ import torch
 from . import native_runtime as nr
 from . import torch_ops as ops
 
-
-def _default_capture_probe() -> bool:
-    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+DEFAULT_TOKEN_BUDGET = 8192
 
 
-class CaptureSafeScratch:
-    """Persistent device buffers keyed by (device index, key)."""
+class StepArena:
+    """A single uint8 device allocation divided into named, 256-byte aligned regions.
 
-    def __init__(self, capture_probe=None):
-        self._buffers: dict = {}
-        self._capture_probe = capture_probe or _default_capture_probe
+    ``plan`` maps a region name to ``(dtype, element count at the token budget)``. ``take(name, n)``
+    returns the first ``n`` elements of the region as a typed 1-D tensor; asking for more than was
+    planned raises ``ValueError`` (the budget was too small), never reallocates."""
 
-    def keys(self):
-        return list(self._buffers.keys())
+    def __init__(self, plan: dict, device):
+        self.device = torch.device(device)
+        self._regions = {}
+        offset = 0
+        for name, (dtype, count) in plan.items():
+            nbytes = count * torch.empty((), dtype=dtype).element_size()
+            self._regions[name] = (offset, dtype, count)
+            offset += (nbytes + 255) // 256 * 256
+        self.nbytes = offset
+        self._store = torch.empty(max(offset, 256), dtype=torch.uint8, device=self.device)
 
-    def get(self, key, count: int, *, dtype, device, capacity: int | None = None,
-            name: str = "scratch") -> torch.Tensor:
-        if count < 0:
-            raise ValueError(f"{name}: count must be non-negative, got {count}")
-        k = (device.index, key)
-        store = self._buffers.get(k)
-        if store is not None and store.numel() >= count:
-            return store[:count]
-        if self._capture_probe():
-            cap = 0 if store is None else store.numel()
-            raise RuntimeError(
-                f"[vkernels_b200] persistent {name} (dev={device.index}, key={key!r}, cap={cap}) "
-                f"is too small for {count} elements and a CUDA-graph capture is active - refusing "
-                f"to grow (the captured graph references the old storage). Size it before capture.")
-        cap = max(count, capacity) if capacity is not None else count
-        store = torch.empty(cap, dtype=dtype, device=device)
-        self._buffers[k] = store
-        return store[:count]
-
-    def reset(self) -> None:
-        self._buffers.clear()
+    def take(self, name: str, count: int) -> torch.Tensor:
+        offset, dtype, cap = self._regions[name]
+        if count < 0 or count > cap:
+            raise ValueError(f"[vkernels_b200] region {name!r} holds {cap} elements, {count} requested: "
+                             f"the layer was built for a smaller token budget (max_tokens)")
+        size = torch.empty((), dtype=dtype).element_size()
+        return self._store[offset: offset + count * size].view(dtype)
 
 
-def max_num_tokens_hint() -> int:
-    """Token budget used to size persistent scratch (reference vllm_experts.py:254-271)."""
-    for k in ("MAX_NUM_BATCHED_TOKENS", "VLLM_MAX_NUM_BATCHED_TOKENS"):
-        v = os.environ.get(k)
-        if v:
-            try:
-                n = int(v)
-                if n > 0:
-                    return n
-            except ValueError:
-                pass
-    return 8192
+@contextlib.contextmanager
+def _region(name: str):
+    """Profiler range around one phase of a layer call, named like the reference binding's
+    regions (``moe:apply.gpu_align``, ``moe:apply.launch``; vllm_experts.py:897,1063) so its
+    per-call profile tooling reads both. Off unless VK_MOE_NVTX=1: a range costs a microsecond
+    of host time per phase, which a decode step does not have to spare."""
+    if not _NVTX:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
+_NVTX = os.environ.get("VK_MOE_NVTX", "0") == "1"
+
+
+def set_profile_ranges(on: bool) -> None:
+    global _NVTX
+    _NVTX = bool(on)
 
 
 class FusedMoEMxfp4:
@@ -80,7 +86,7 @@ class FusedMoEMxfp4:
                  scaling: float = 1.0, n_group: int = 1, topk_group: int = 1, n_shared: int = 0,
                  swiglu_limit: float = 0.0, activation: int = ops.moe_fused_mxfp4.SWIGLU,
                  beta: float = 4.0, linear_beta: float = 25.0, b13=None, b2=None,
-                 max_tokens: int | None = None, block_size: int = 16):
+                 max_tokens: int = DEFAULT_TOKEN_BUDGET, block_size: int = 16):
         ops.same_gpu_contiguous(w13, w13_scale, w2, w2_scale)
         self.w13, self.w13_scale, self.w2, self.w2_scale = w13, w13_scale, w2, w2_scale
         self.b13, self.b2 = b13, b2
@@ -101,41 +107,46 @@ class FusedMoEMxfp4:
         # layer holds only a slice of them
         self.n_router = self.n_routed if router_weight is None else router_weight.shape[0]
         self.block_size = block_size
-        self.max_tokens = max_tokens or max_num_tokens_hint()
-        self.scratch = CaptureSafeScratch()
+        self.max_tokens = int(max_tokens or DEFAULT_TOKEN_BUDGET)
+        self.capture_stream = None
         self._reserve()
 
     # -- sizing ------------------------------------------------------------------------------
     def _em_bound(self, T: int) -> int:
         return ops.align_em_bound(T, self.slots, self.n_experts_total, self.block_size)
 
-    def _reserve(self) -> None:
+    def _workspace_bytes(self) -> int:
         T = self.max_tokens
-        em = self._em_bound(T)
-        lib = nr.load_library()
-        with torch.cuda.device(self.device):
-            need = lib.vk_cuda_moe_workspace_bytes(em, self.hidden, self.ispp, self.n_experts_total,
-                                                   T * self.slots)
-            nr.check(lib.vk_cuda_moe_reserve_workspace(need), "reserve_workspace")
-        self._buffers(T)  # pins every persistent buffer at the budget
+        return nr.load_library().vk_cuda_moe_workspace_bytes(self._em_bound(T), self.hidden, self.ispp,
+                                                             self.n_experts_total, T * self.slots)
+
+    def _reserve(self) -> None:
+        """Everything a step needs, allocated once: the library scratch of the current stream and
+        the layer's own arena, both at the token budget."""
+        T = self.max_tokens
+        cap_em = self._em_bound(T)
+        ops.reserve_workspace(self._workspace_bytes(), self.device)
+        self.arena = StepArena({
+            "logits": (torch.float32, T * self.n_router),
+            "ids": (torch.int32, T * self.slots),
+            "w": (torch.float32, T * self.slots),
+            "sids": (torch.int32, cap_em),
+            "eids": (torch.int32, cap_em // self.block_size),
+            "out_em": (torch.int32, 1),
+            "act": (torch.bfloat16, cap_em * self.ispp),
+            "out": (torch.float32, T * self.hidden),
+            "x": (torch.bfloat16, T * self.hidden),
+            "y": (torch.bfloat16, T * self.hidden),
+        }, self.device)
 
     def _buffers(self, T: int):
-        d, s, cap_t = self.device, self.scratch, self.max_tokens
-        cap_em = self._em_bound(cap_t)
         em = self._em_bound(T)
-        g = lambda key, n, dt, cap: s.get(key, n, dtype=dt, device=d, capacity=cap, name=str(key))
-        return {
-            "logits": g("logits", T * self.n_router, torch.float32, cap_t * self.n_router),
-            "ids": g("ids", T * self.slots, torch.int32, cap_t * self.slots),
-            "w": g("w", T * self.slots, torch.float32, cap_t * self.slots),
-            "sids": g("sids", em, torch.int32, cap_em),
-            "eids": g("eids", em // self.block_size, torch.int32, cap_em // self.block_size),
-            "out_em": g("out_em", 1, torch.int32, 1),
-            "act": g("act", em * self.ispp, torch.bfloat16, cap_em * self.ispp),
-            "out": g("out", T * self.hidden, torch.float32, cap_t * self.hidden),
-            "x": g("x", T * self.hidden, torch.bfloat16, cap_t * self.hidden),
-            "y": g("y", T * self.hidden, torch.bfloat16, cap_t * self.hidden),
-        }
+        a = self.arena
+        return {"logits": a.take("logits", T * self.n_router), "ids": a.take("ids", T * self.slots),
+                "w": a.take("w", T * self.slots), "sids": a.take("sids", em),
+                "eids": a.take("eids", em // self.block_size), "out_em": a.take("out_em", 1),
+                "act": a.take("act", em * self.ispp), "out": a.take("out", T * self.hidden),
+                "x": a.take("x", T * self.hidden), "y": a.take("y", T * self.hidden)}
 
     # -- stages ------------------------------------------------------------------------------
     def route(self, x: torch.Tensor, bufs=None, logits: torch.Tensor | None = None):
@@ -165,21 +176,24 @@ class FusedMoEMxfp4:
         T = x.shape[0]
         bufs = bufs or self._buffers(T)
         em = self._em_bound(T)
-        sids, eids, _ = ops.moe_align_block_size(
-            topk_ids, self.n_experts_total, self.block_size, max_EM=em,
-            out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
+        with _region("moe:apply.gpu_align"):
+            sids, eids, _ = ops.moe_align_block_size(
+                topk_ids, self.n_experts_total, self.block_size, max_EM=em,
+                out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
         out = bufs["out"].view(T, self.hidden)
-        out.zero_()
-        ops.fused_moe_mxfp4_into(out, bufs["act"], x, self.w13, self.w13_scale, self.w2,
-                                 self.w2_scale, topk_w.reshape(-1), sids, eids,
-                                 top_k=topk_ids.shape[1], block_size=self.block_size,
-                                 swiglu_limit=self.swiglu_limit, activation=self.activation,
-                                 beta=self.beta, linear_beta=self.linear_beta, b13=self.b13,
-                                 b2=self.b2)
+        with _region("moe:apply.launch"):
+            out.zero_()
+            ops.fused_moe_mxfp4_into(out, bufs["act"], x, self.w13, self.w13_scale, self.w2,
+                                     self.w2_scale, topk_w.reshape(-1), sids, eids,
+                                     top_k=topk_ids.shape[1], block_size=self.block_size,
+                                     swiglu_limit=self.swiglu_limit, activation=self.activation,
+                                     beta=self.beta, linear_beta=self.linear_beta, b13=self.b13,
+                                     b2=self.b2)
         if return_fp32:
             return out
         y = bufs["y"].view(T, self.hidden) if out_bf16 is None else out_bf16
-        y.copy_(out)
+        with _region("moe:apply.convert"):
+            y.copy_(out)
         return y
 
     def experts_rows(self, a_rows, out_rows, topk_ids, topk_w):
@@ -202,7 +216,8 @@ class FusedMoEMxfp4:
         """route -> align -> gate/up -> down+combine, all on the current stream."""
         ops.require(x.dim() == 2 and x.shape[1] == self.hidden, "x must be [T, hidden]")
         bufs = self._buffers(x.shape[0])
-        ids, w = self.route(x, bufs, logits=logits)
+        with _region("moe:apply.route"):
+            ids, w = self.route(x, bufs, logits=logits)
         return self.experts(x, ids, w, bufs, out_bf16=out_bf16)
 
     __call__ = forward
@@ -213,9 +228,12 @@ class FusedMoEMxfp4:
         then and leaves the result in ``y``. A decode step is a dozen short kernels; replaying
         them as one graph removes the launch gaps between them. Everything the step needs is
         allocated before the capture (two eager warm-up calls)."""
-        side = torch.cuda.Stream(device=self.device)
+        side = self.capture_stream or torch.cuda.Stream(device=self.device)
+        self.capture_stream = side
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
+            # the library scratch belongs to a stream: this one needs its block before the capture
+            ops.reserve_workspace(self._workspace_bytes(), self.device)
             for _ in range(2):
                 self.forward(x)
         torch.cuda.current_stream(self.device).wait_stream(side)

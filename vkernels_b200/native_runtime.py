@@ -48,7 +48,13 @@ _SIGNATURES = {
     "vk_cuda_moe_get_impl": (c_int, []),
     "vk_cuda_moe_workspace_bytes": (c_size_t, [c_int] * 5),
     "vk_cuda_moe_reserve_workspace": (c_int, [c_size_t]),
+    "vk_cuda_moe_reserve_workspace_on": (c_int, [c_size_t, c_void_p]),
+    "vk_cuda_moe_release_workspaces": (c_int, []),
+    "vk_cuda_moe_workspace_live_bytes": (c_size_t, []),
     "vk_cuda_moe_kernel_status": (c_int, []),
+    "vk_cuda_moe_reset_kernel_status": (c_int, []),
+    "vk_cuda_moe_test_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p]),
+    "vk_cuda_mxfp4_dequant_rows_path": (c_int, [c_void_p] * 3 + [c_int] * 3 + [c_void_p]),
     "vk_cuda_moe_timing_begin": (c_int, [c_int]),
     "vk_cuda_moe_timing_end": (c_int, [c_void_p] * 3),
     "vk_cuda_mxfp4_dequant_rows": (c_int, [c_void_p] * 3 + [c_int] * 2 + [c_void_p]),
@@ -64,6 +70,7 @@ _SIGNATURES = {
     "vk_cuda_moe_ep_pack_meta_peer": (c_int, [c_void_p] * 2 + [c_int] * 5 + [c_void_p] * 4 + [c_int, c_void_p]),
     "vk_cuda_moe_ep_unpack_meta_peer": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_void_p] * 2 + [c_int] +
                                         [c_void_p] * 5),
+    "vk_cuda_moe_ep_flag_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p]),
     "vk_cuda_fused_moe_mxfp4_rows": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
                                      [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p,
                                       c_int, c_void_p]),

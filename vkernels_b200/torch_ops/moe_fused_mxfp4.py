@@ -117,8 +117,23 @@ def route_topk(logits: torch.Tensor, top_k: int, *, bias: torch.Tensor | None = 
     return ids, w
 
 
-def mxfp4_dequant_rows(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """[rows, K/2] uint8 + [rows, K/32] uint8 -> [rows, K] bf16 (the kernels' own decoder)."""
+def reset_kernel_status() -> None:
+    """Synchronise and clear the status word of the current device."""
+    nr.check(nr.load_library().vk_cuda_moe_reset_kernel_status(), "reset_kernel_status")
+
+
+def reserve_workspace(nbytes: int, device) -> None:
+    """Allocate the library scratch of the CURRENT stream of `device` ahead of time (the layer
+    launchers then allocate nothing; mandatory before capturing that stream)."""
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        nr.check(nr.load_library().vk_cuda_moe_reserve_workspace_on(
+            int(nbytes), torch.cuda.current_stream(device).cuda_stream), "reserve_workspace")
+
+
+def mxfp4_dequant_rows(packed: torch.Tensor, scale: torch.Tensor, path: str = "permute") -> torch.Tensor:
+    """[rows, K/2] uint8 + [rows, K/32] uint8 -> [rows, K] bf16 through one of the kernels' own
+    decoders: "permute" (CTA-pair form) or "table" (lone-CTA form)."""
     require(packed.dtype == torch.uint8 and scale.dtype == torch.uint8, "uint8 inputs expected")
     same_gpu_contiguous(packed, scale)
     rows, kb = packed.shape
@@ -126,8 +141,9 @@ def mxfp4_dequant_rows(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
     require(scale.shape == (rows, K // 32), "scale must be [rows, K/32]")
     out = torch.empty((rows, K), dtype=torch.bfloat16, device=packed.device)
     with torch.cuda.device(packed.device):
-        nr.check(nr.load_library().vk_cuda_mxfp4_dequant_rows(_ptr(packed), _ptr(scale), _ptr(out),
-                                                             rows, K, _stream(packed)),
+        sel = {"permute": 0, "table": 1}[path]
+        nr.check(nr.load_library().vk_cuda_mxfp4_dequant_rows_path(_ptr(packed), _ptr(scale), _ptr(out),
+                                                                  rows, K, sel, _stream(packed)),
                  "mxfp4_dequant_rows")
     return out
 
