@@ -366,8 +366,9 @@ def run_single_gpu(args, cfg, T):
     # outside the timed region: this very layer object against the CPU oracle on a token sample
     y0 = layer(A, logits=logits)
     ids0, tw0 = layer.route(A, logits=logits)
-    parity = oracle_parity(cfg, A, y0, ids0, tw0, w, args.parity_tokens, cfg.seed, logits=logits, router=r)
-    if not parity["ok"]:
+    parity = {"skipped": True, "ok": None} if args.skip_parity else \
+        oracle_parity(cfg, A, y0, ids0, tw0, w, args.parity_tokens, cfg.seed, logits=logits, router=r)
+    if parity["ok"] is False:
         print(json.dumps({"error": "parity check against the CPU oracle failed", "parity": parity}), flush=True)
         sys.exit(3)
 
@@ -403,7 +404,7 @@ def run_single_gpu(args, cfg, T):
     # end to end: pinned host activations in, pinned host bf16 result out, copies inside the region
     xh = A.cpu().pin_memory()
     yh = torch.empty((T, cfg.H), dtype=torch.bfloat16).pin_memory()
-    if logits is None:
+    if logits is None and not args.skip_parity:
         e2e_step = lambda: layer.forward_host(xh, yh)
         for _ in range(args.warmup):
             e2e_step()
@@ -575,6 +576,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the batch size of the workload")
     ap.add_argument("--cpu-tokens", type=int, default=256, help="token sample of the CPU baseline")
     ap.add_argument("--parity-tokens", type=int, default=48, help="tokens per rank checked against the CPU oracle")
+    ap.add_argument("--skip-parity", action="store_true",
+                    help="profiling runs only: no oracle check and no end-to-end leg (single GPU)")
     ap.add_argument("--weak", action="store_true", help="multi-GPU: keep the batch PER RANK fixed (weak scaling)")
     ap.add_argument("--no-decode-sweep", dest="decode_sweep", action="store_false")
     args = ap.parse_args()

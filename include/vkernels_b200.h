@@ -134,6 +134,21 @@ int vk_cuda_fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13,
                                      const float* b13, const float* b2, int block_size,
                                      void* stream);
 
+/* The layer with a bf16 result and an ordered, atomic-free combine (no device-side counterpart
+ * in the reference for this path; the idea is its W4A4 scatter-reduce's inverse-permutation
+ * gather, src/c/vkernels/kernels/moe_aux.hpp:150-155). Arguments as vk_hip_fused_moe_mxfp4 with
+ * y [M, hidden] bf16 in place of the fp32 `out`: y is OVERWRITTEN with bf16(sum over the token's
+ * experts in ascending expert order of (act @ w2^T + b2) * w), the order in which the CPU oracle
+ * adds (moe_fused.cpp:539-562). Bit-reproducible from run to run; nothing to zero before or
+ * convert after the call. At most 32 slots per token. The library scratch of the stream must
+ * hold vk_cuda_moe_workspace_bytes_bf16(...) bytes (EM * hidden fp32 more than the plain form). */
+int vk_cuda_fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+                                 const uint8_t* w2_scale, const float* topk_w, uint16_t* act_scratch, uint16_t* y,
+                                 int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                                 const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
+                                 float linear_beta, const float* b13, const float* b2, int block_size, void* stream);
+size_t vk_cuda_moe_workspace_bytes_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N);
+
 /* Router. The reference has no router in this path; semantics follow its GPU
  * routing ops (src/python/vkernels/torch_ops/tokenspeed_amd/routing.py:58-145,
  * torch_ops/glm_router.py:43-88,184-262).
@@ -150,6 +165,16 @@ int vk_cuda_moe_router_logits(const uint16_t* x, const float* wr, float* logits,
 int vk_cuda_moe_route_topk(const float* logits, const float* bias, int T, int E, int k,
                            int sigmoid, int n_group, int topk_group, int renorm, float scaling,
                            int n_shared, int32_t* ids, float* w, void* stream);
+
+/* vk_cuda_moe_route_topk followed by vk_hip_moe_align_block_size (no expert map, num_experts =
+ * local_n = E + n_shared) as one single-CTA kernel, for at most 1024 routed slots (T * (k +
+ * n_shared)) - the decode regime, where each launch removed from the step counts. Same outputs
+ * as the two calls, bit for bit. The reference's precedent for fusing the router into the layer's
+ * front end: src/python/vkernels/torch_ops/glm_router_dense.py:112-150, glm_router.py:205-262. */
+int vk_cuda_moe_route_align_small(const float* logits, const float* bias, int T, int E, int k, int sigmoid,
+                                  int n_group, int topk_group, int renorm, float scaling, int n_shared,
+                                  int block_size, int max_EM, int32_t* ids, float* w, int32_t* sorted_ids,
+                                  int32_t* expert_ids, int32_t* out_em, void* stream);
 
 /* 0 = tcgen05 tensor-core kernels (default), 1 = CUDA-core cross-check kernels
  * that add in the CPU oracle's order. Also settable with VK_MOE_IMPL=simt. */

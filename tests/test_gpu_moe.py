@@ -272,6 +272,36 @@ def test_full_size_properties_c2():
     assert_close_bf16(to_np(moved), to_np(base[perm]), "token permutation")
 
 
+@pytest.mark.parametrize("name,T", [("c0", 64), ("c1", 8), ("c1", 128), ("c4", 256), ("c2", 1024)])
+def test_bf16_form_with_ordered_combine(name, T):
+    """vk_cuda_fused_moe_mxfp4_bf16: result within the layer's tolerance of the oracle, equal
+    (to bf16 rounding) to the atomic form, bit-identical from run to run, and with biases."""
+    cfg = syn.CONFIGS[name]
+    w, A, r = make_case(cfg, T, backend="torch")
+    logits = syn.make_zipf_logits(cfg, T, device=DEV) if cfg.zipf_alpha else None
+    ids_np, tw_np, _ = oracle_route(cfg, A, r, logits=None if logits is None else to_np(logits))
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    E = w["w13"].shape[0]
+    rng = np.random.default_rng(T)
+    b13 = torch.from_numpy(rng.standard_normal((E, 2 * cfg.I)).astype(np.float32) * 0.1).to(DEV)
+    b2 = torch.from_numpy(rng.standard_normal((E, cfg.H)).astype(np.float32) * 0.1).to(DEV)
+    sids, eids, _ = ops.moe_align_block_size(ids, E, 16)
+    act = torch.zeros((sids.numel(), cfg.I), dtype=torch.bfloat16, device=DEV)
+    ys = []
+    for _ in range(2):
+        y = torch.full((T, cfg.H), 7.0, dtype=torch.bfloat16, device=DEV)    # must be overwritten, not added to
+        ops.fused_moe_mxfp4_bf16_into(y, act, A, w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], tw.reshape(-1).contiguous(),
+                                      sids, eids, top_k=ids.shape[1], swiglu_limit=cfg.swiglu_limit, b13=b13, b2=b2)
+        torch.cuda.synchronize()
+        ops.kernel_status()
+        ys.append(y.clone())
+    assert torch.equal(ys[0], ys[1]), "the ordered combine must be bit-reproducible"
+    tokens = None if T <= 64 else np.sort(rng.choice(T, 48, replace=False))
+    ref = oracle_layer(A, w, ids, tw, tokens=tokens, swiglu_limit=cfg.swiglu_limit, b13=to_np(b13), b2=to_np(b2))
+    got = to_np(ys[0].float())
+    assert_close_bf16(got if tokens is None else got[tokens], ref, f"bf16 form {name} T={T}", got_is_bf16=True)
+
+
 def test_host_pointer_abi():
     """vk_fused_moe_mxfp4 with HOST buffers (the CPU entry point's signature): copies in,
     kernels, copies out; accumulates into `out` like the reference."""

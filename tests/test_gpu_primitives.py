@@ -164,6 +164,23 @@ def test_routing_zipf_logits():
     _check_route(cfg, 4096, logits=syn.make_zipf_logits(cfg, 4096, device=DEV))
 
 
+@pytest.mark.parametrize("name,T", [("c0", 64), ("c1", 1), ("c1", 128), ("c3", 100), ("c4", 16)])
+def test_fused_route_align_equals_the_two_kernels(name, T):
+    """The single-CTA small-batch kernel (router top-k + alignment) produces, bit for bit, what
+    route_topk followed by moe_align_block_size produce."""
+    cfg = syn.CONFIGS[name]
+    r = syn.make_router(cfg, device=DEV)
+    A = syn.make_activations(cfg, T, device=DEV)
+    lg = syn.make_zipf_logits(cfg, T, device=DEV) if cfg.zipf_alpha else ops.router_logits(A, r["wr"])
+    kw = dict(bias=r["bias"], sigmoid=cfg.routing == "sigmoid_group", n_group=cfg.n_group, topk_group=cfg.topk_group,
+              renorm=cfg.renorm, scaling=cfg.scaling, n_shared=cfg.shared_experts)
+    ids, w = ops.route_topk(lg, cfg.top_k, **kw)
+    s, e, em = ops.moe_align_block_size(ids, cfg.n_weight_experts, 16)
+    ids2, w2, s2, e2, em2 = ops.route_align_small(lg, cfg.top_k, block_size=16, **kw)
+    assert torch.equal(ids, ids2) and torch.equal(w, w2)
+    assert torch.equal(s, s2) and torch.equal(e, e2) and int(em.item()) == int(em2.item())
+
+
 def test_routing_golden():
     import os
     g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "routing.npz"))

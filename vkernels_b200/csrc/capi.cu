@@ -158,6 +158,21 @@ int vk_cuda_fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13,
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 
+int vk_cuda_fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+                                 const uint8_t* w2_scale, const float* topk_w, uint16_t* act_scratch, uint16_t* y,
+                                 int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                                 const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
+                                 float linear_beta, const float* b13, const float* b2, int block_size, void* stream) {
+  VK_TRY
+  vkc::fused_moe_mxfp4_bf16(A, w13, w13_scale, w2, w2_scale, topk_w, act_scratch, y, M, hidden, ispp, top_k,
+                            sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2,
+                            block_size, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+size_t vk_cuda_moe_workspace_bytes_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N) {
+  return vkc::workspace_bytes_required_bf16(max_EM, hidden, ispp, n_local_experts, N);
+}
+
 int vk_cuda_moe_router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H,
                               int E, void* stream) {
   VK_TRY
@@ -171,6 +186,16 @@ int vk_cuda_moe_route_topk(const float* logits, const float* bias, int T, int E,
   VK_TRY
   vkc::route_topk(logits, bias, T, E, k, sigmoid, n_group, topk_group, renorm, scaling, n_shared,
                   ids, w, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_route_align_small(const float* logits, const float* bias, int T, int E, int k, int sigmoid,
+                                  int n_group, int topk_group, int renorm, float scaling, int n_shared,
+                                  int block_size, int max_EM, int32_t* ids, float* w, int32_t* sorted_ids,
+                                  int32_t* expert_ids, int32_t* out_em, void* stream) {
+  VK_TRY
+  vkc::route_align_small(logits, bias, T, E, k, sigmoid, n_group, topk_group, renorm, scaling, n_shared, block_size,
+                         max_EM, ids, w, sorted_ids, expert_ids, out_em, stream);
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -137,6 +138,23 @@ __device__ __forceinline__ void fill_dequant_lut(uint32_t* lut, int tid, int n_t
     lut[i] = e2m1_bf16_bits(byte & 15u) | (e2m1_bf16_bits(byte >> 4) << 16);
   }
 }
+
+// Eight packed nibbles -> eight e5m2 bytes in K order (out[0] = k0..k3, out[1] = k4..k7). Every
+// value of the layer's table is exact in e5m2, inf and NaN included: magnitudes
+// {00, 34, 3C, 3E, 40, 42, 7C, 7E}, sign in bit 7. A byte permute with the 3-bit magnitudes as
+// selectors looks four nibbles up at once; a second permute in sign-replication mode brings the
+// four sign bits to the byte tops.
+__device__ __forceinline__ void expand8_e5m2(uint32_t w, uint32_t out[2]) {
+  constexpr uint32_t P0 = 0x3E3C3400u, P1 = 0x7E7C4240u;
+  const uint32_t m = w & 0x77777777u;
+  const uint32_t t = w << 4;
+  const uint32_t a0 = prmt(P0, P1, m), a1 = prmt(P0, P1, m >> 16);
+  const uint32_t s0 = prmt(w, t, 0x9D8Cu), s1 = prmt(w, t, 0xBFAEu);
+  out[0] = a0 | (s0 & 0x80808080u);
+  out[1] = a1 | (s1 & 0x80808080u);
+}
+// value of an e5m2 byte
+__device__ __forceinline__ float e5m2_to_f32(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)(b << 8))); }
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) { return __uint_as_float(b16 << 16); }
 

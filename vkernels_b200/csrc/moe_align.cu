@@ -16,92 +16,13 @@
 
 #include "common.cuh"
 #include "moe_fused.hpp"
+#include "moe_prep.cuh"
 
 namespace vkernels::kernels::cuda {
 
 namespace {
 
-constexpr int kChunk = 1024;   // entries per chunk = threads per CTA
-constexpr int kWarps = kChunk / 32;
-
-__device__ __forceinline__ int local_expert(const int32_t* topk_ids, const int32_t* expert_map,
-                                            int i, int N, int num_experts, int local_n) {
-  if (i >= N) return -1;
-  int e = topk_ids[i];
-  if (e < 0 || e >= num_experts) return -1;
-  if (expert_map != nullptr) e = expert_map[e];
-  return (e < 0 || e >= local_n) ? -1 : e;
-}
-
-// Rank of each thread's entry among the chunk's entries with the same expert
-// (entries ordered by thread index), plus the chunk histogram in hist[0][*].
-//   warp_hist: [kWarps + 1][local_n] ints of shared memory.
-// On return warp_hist[w][e] = number of entries of expert e in warps < w and
-// warp_hist[kWarps][e] = the chunk total.
-__device__ __forceinline__ int chunk_rank(int le, int local_n, int* warp_hist) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < (kWarps + 1) * local_n; i += kChunk) warp_hist[i] = 0;
-  __syncthreads();
-  // peers = lanes of this warp holding the same expert (le = -1 groups too, ignored below)
-  const unsigned peers = __match_any_sync(0xFFFFFFFFu, le);
-  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
-  if (le >= 0 && rank_in_warp == 0) warp_hist[warp * local_n + le] = __popc(peers);
-  __syncthreads();
-  // exclusive scan over warps, one thread per expert
-  for (int e = tid; e < local_n; e += kChunk) {
-    int run = 0;
-    for (int w = 0; w < kWarps; ++w) {
-      int c = warp_hist[w * local_n + e];
-      warp_hist[w * local_n + e] = run;
-      run += c;
-    }
-    warp_hist[kWarps * local_n + e] = run;
-  }
-  __syncthreads();
-  return le >= 0 ? warp_hist[warp * local_n + le] + rank_in_warp : 0;
-}
-
-// Exclusive scan of padded expert sizes by one CTA; writes expert_ids for the
-// real blocks, the row offset of every expert, and *out_em.
-//   count[e] : entries of expert e (shared or global)
-//   offset[e]: receives the first sorted row of expert e
-__device__ __forceinline__ void scan_experts(const int* count, int* offset, int local_n,
-                                             int block_size, int max_EM, int32_t* expert_ids,
-                                             int32_t* out_em, int* s_tmp /* [kChunk] */) {
-  const int tid = threadIdx.x;
-  // each thread owns a contiguous slice of experts
-  const int per = (local_n + kChunk - 1) / kChunk;
-  const int e0 = tid * per, e1 = min(local_n, e0 + per);
-  int mine = 0;
-  for (int e = e0; e < e1; ++e) mine += ((count[e] + block_size - 1) / block_size) * block_size;
-  s_tmp[tid] = mine;
-  __syncthreads();
-  // Hillis-Steele inclusive scan over the 1024 per-thread sums
-  for (int d = 1; d < kChunk; d <<= 1) {
-    int v = (tid >= d) ? s_tmp[tid - d] : 0;
-    __syncthreads();
-    s_tmp[tid] += v;
-    __syncthreads();
-  }
-  int run = s_tmp[tid] - mine;
-  const int max_blocks = max_EM / block_size;
-  for (int e = e0; e < e1; ++e) {
-    offset[e] = run;
-    const int nb = (count[e] + block_size - 1) / block_size;
-    for (int b = 0; b < nb; ++b) {
-      const int blk = run / block_size + b;
-      if (blk < max_blocks) expert_ids[blk] = e;
-    }
-    run += nb * block_size;
-  }
-  if (tid == kChunk - 1) {
-    int EM = s_tmp[kChunk - 1];
-    if (EM == 0) EM = block_size;
-    if (EM > max_EM) EM = max_EM;
-    *out_em = EM;
-  }
-  __syncthreads();
-}
+using namespace prep;
 
 // ------------------------------ one CTA, N <= kChunk -------------------------
 __global__ void __launch_bounds__(kChunk)

@@ -59,6 +59,20 @@ void fused_moe_mxfp4_sorted_w(const uint16_t* A, const uint8_t* w13, const uint8
                               int activation, float beta, float linear_beta, const float* b13,
                               const float* b2, int block_size, void* stream);
 
+// The layer with a bf16 result and an ORDERED combine: the down GEMM leaves plain fp32 partial
+// rows in the library scratch and a second kernel adds each token's rows in ascending expert
+// order - the order of the CPU definition (reference moe_fused.cpp:539-562; the atomic-free
+// inverse-permutation gather the reference describes for its W4A4 path, moe_aux.hpp:150-155) -
+// and writes y [M, hidden] bf16, overwriting it. Deterministic from run to run; no fp32 output to
+// zero beforehand or convert afterwards, which is what a decode step saves. The scratch grows by
+// EM * hidden fp32 (workspace_bytes_required_bf16).
+void fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+                          const uint8_t* w2_scale, const float* topk_w, uint16_t* act_scratch, uint16_t* y_bf16,
+                          int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
+                          const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
+                          float linear_beta, const float* b13, const float* b2, int block_size, void* stream);
+size_t workspace_bytes_required_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N);
+
 // Row addresses instead of base pointers: token m's activation row is read at a_rows[m] and
 // its result is added at out_rows[m] (hidden bf16 / fp32 values each, 16-byte aligned). The rows
 // may live in another GPU's memory mapped into this process (peer loads and reductions over
@@ -129,6 +143,14 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
 void route_topk(const float* logits, const float* bias, int T, int E, int k, int sigmoid,
                 int n_group, int topk_group, int renorm, float scaling, int n_shared,
                 int32_t* ids, float* w, void* stream);
+
+// route_topk followed by moe_align_block_size (no expert map; num_experts = local_n = E +
+// n_shared) as ONE single-CTA kernel, for batches of at most 1024 routed slots (T * (k +
+// n_shared)): the decode regime, where every launch removed from the step counts.
+void route_align_small(const float* logits, const float* bias, int T, int E, int k, int sigmoid, int n_group,
+                       int topk_group, int renorm, float scaling, int n_shared, int block_size, int max_EM,
+                       int32_t* ids, float* w, int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_em,
+                       void* stream);
 
 // Library-owned device scratch (tile lists, the gathered activation rows of the gate/up GEMM,
 // alignment histograms): one block per (device, stream), so layer calls on different streams do

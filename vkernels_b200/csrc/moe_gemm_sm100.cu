@@ -52,7 +52,10 @@
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
+#include <string>
 #include <vector>
+
+#include <cuda_fp8.h>
 
 #include "common.cuh"
 #include "moe_fused.hpp"
@@ -80,9 +83,11 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 // dequant sets and two epilogue sets (the accumulator drains twice as fast, which is what its
 // MMA issuer waits for); a lone CTA (decode) runs three dequant sets and one epilogue set (its
 // epilogue is a few rounds, its bound is the expansion).
-constexpr int dequant_sets(int ctas) { return ctas == 2 ? 2 : 3; }   // dequant warps per TMEM lane quarter
+// The fp8 form (see below) runs four dequant sets: its expansion is bound by the integer pipe, and
+// four warps per scheduler keep that pipe fed while the others wait on barriers.
+constexpr int dequant_sets(int ctas, bool mx = false) { return mx ? 4 : (ctas == 2 ? 2 : 3); }   // dequant warps per TMEM lane quarter
 constexpr int epi_sets(int ctas) { return ctas == 2 ? 2 : 1; }       // epilogue warps per lane quarter
-constexpr int kThreads = (4 + 4 * 4) * 32;
+constexpr int block_threads(int ctas, bool mx) { return (4 + 4 * (dequant_sets(ctas, mx) + epi_sets(ctas))) * 32; }
 constexpr int kTmemCols = 512;
 constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
 constexpr int kEpiStageBytes = 2 * 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds per set, up to two sets)
@@ -105,6 +110,7 @@ struct TokTile {
 };
 
 struct GemmParams {
+  const float* tok_scale;     // fp8 form: power-of-two scale of every sorted token row [EM]
   const uint8_t* w_scale;     // [E, n_wrows, K/32]
   const float* bias;          // gate/up: [E, 2*n_feat]; down: [E, n_feat]; or null
   const float* topk_w;        // down only
@@ -115,6 +121,7 @@ struct GemmParams {
   float* raw;                 // optional: plain fp32 result rows [EM, raw_ld] instead of the fused epilogue
   int raw_ld;                 //   (the tensor-parallel stage split: the caller reduces across ranks first)
   int k_base;                 // first column of the token rows this launch reduces over (K-sharded weights)
+  int piece_rows;             // fp8 form: rows between the two e4m3 pieces of the token operand
   const TokTile* tiles;
   const int* n_tiles;
   int K;                      // reduction length (hidden for gate/up, ispp for down)
@@ -261,6 +268,37 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
       "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
       "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
       "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+__device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b),
+               "r"(c), "r"(d)
+               : "memory");
+}
+// D[tmem] (+)= (A[tmem] x 2^sfa) * (B[smem] x 2^sfb): e5m2 x e4m3 with one ue8m0 scale factor per
+// 32 K-elements and row, both scale-factor operands in tensor memory; K = 32 per instruction.
+__device__ __forceinline__ void tc_mma_mx(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], [%1], %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() {
@@ -430,6 +468,12 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128.
+// Block-scaled instruction descriptor: A e5m2 (format 1, bits 7-9), B e4m3 (format 0), both
+// K-major, N >> 3 at bit 17, ue8m0 scale factors (bit 23), M >> 4 at bit 24; the byte of the
+// scale-factor column that holds this K block goes to bits 29-30 (A) and 4-5 (B) per instruction.
+__device__ __forceinline__ uint32_t make_idesc_mx(int n) {
+  return (1u << 7) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+}
 __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
@@ -447,13 +491,14 @@ struct Barriers {
   uint64_t stage_done[kMaxAStages];  // MMA completion of a stage: frees its A slot AND its token slot
   uint64_t b_full[kMaxBStages];
   uint64_t sc_full[2], sc_empty[2];
-  uint64_t acc_full, acc_empty;
+  uint64_t acc_full[2], acc_empty[2];   // the fp8 form alternates between two accumulators
   uint32_t tmem_base;
   int abort_flag;
   // per token column of the current item: gate/up 1 for a real row, 0 for padding;
   // down: address of the token's output row, 0 for padding
   unsigned long long tile_ref[kPairMaxTok];
   float tile_w[kPairMaxTok];
+  float tile_s[kPairMaxTok];   // fp8 form: the token's power-of-two scale
 };
 
 // Ring position: slot index and phase parity, advanced without division.
@@ -476,14 +521,38 @@ struct Ring {
 // per-stage latency (barrier polls + commit) is a few hundred cycles whatever
 // the stage holds, so small token tiles, whose MMAs are short, take long
 // stages: KS = 64 for tiles up to 256 tokens, 128 up to 128, 256 up to 64.
-template <bool GATEUP, int KS, int CTAS>
-__global__ void __launch_bounds__(kThreads, 1)
+//
+// MX (lone CTA, 256-K stages, tiles up to 64 tokens - the decode regime): the fp8 form. The
+// weights are expanded to ONE byte each instead of two: every value of the layer's table
+// {0, .25, 1, 1.5, 2, 3, inf, NaN} is exact in e5m2, and the ue8m0 scale of a 32-element group
+// is not multiplied in at all - it goes to tensor memory as the per-row scale factor of a
+// block-scaled MMA (kind::mxf8f6f4, one scale per 32 K-elements: exactly the MXFP4 grouping).
+// That halves the expansion's instructions and its tensor-memory stores, which is what a decode
+// batch is bound by. The token operand must then be fp8 too: a pre-pass splits every bf16
+// activation x into two e4m3 pieces with x = s * (p1 + p2), s a power of two per token row
+// (8 significant bits = 4 + 4; exact unless an element is more than 2^9 below the row's
+// largest). An MMA with a handful of token columns costs as much as one with 128 (its cost is
+// per instruction), so the two pieces are stacked along N - rows 0..n-1 of the staged tile are
+// p1, rows n..2n-1 are p2 - and ONE MMA per K block yields both partial products in adjacent
+// column ranges of the accumulator; the epilogue adds them and multiplies by s (unit token
+// scale factors inside the MMA).
+// MX = 0: bf16 forms; 32 or 64: the fp8 form for token tiles up to that many rows (with tiles up
+// to 32 rows two accumulators fit tensor memory and alternate between items, so an item's
+// epilogue overlaps the next item's MMAs).
+template <bool GATEUP, int KS, int CTAS, int MX = 0>
+__global__ void __launch_bounds__(block_threads(CTAS, MX != 0), 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
-  constexpr int kAccCols = acc_cols(KS, CTAS);                        // accumulator columns
-  constexpr int kACols = KS / 2;                                      // columns of one A slot
-  constexpr int kAStages = (kTmemCols - kAccCols) / kACols;           // lone CTA: 8, 6, 3; pair: 6, 3
+  static_assert(MX == 0 || ((MX == 32 || MX == 64) && CTAS == 1 && KS == 256), "the fp8 form is a lone CTA with 256-K stages");
+  constexpr int kThreads = block_threads(CTAS, MX != 0);
+  // accumulator columns; the fp8 form keeps the two token pieces side by side
+  constexpr int kAccCols = MX ? 2 * MX : acc_cols(KS, CTAS);
+  constexpr int kAccBufs = MX == 32 ? 2 : 1;
+  constexpr int kSfbCol = kAccBufs * kAccCols;                        // fp8 form: 4 columns of unit token scale factors
+  constexpr int kSlot0 = MX ? kSfbCol + 8 : kAccCols;                 // first A slot
+  constexpr int kACols = MX ? KS / 4 + 8 : KS / 2;                    // columns of one A slot (fp8: 64 of values + 8 of scale factors)
+  constexpr int kAStages = (kTmemCols - kSlot0) / kACols;             // lone CTA: 8, 6, 3 (fp8: 5); pair: 6, 3
   constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
   constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
   static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
@@ -497,7 +566,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // expected on the same barrier the dequant warps arrive on, so the MMA issuer polls a single
   // barrier per stage.
   constexpr bool kMerged = CTAS == 2;
-  constexpr int kDequantSets = dequant_sets(CTAS), kEpiSets = epi_sets(CTAS);
+  constexpr int kMxSplit = 1;   // fp8 form: dequant warps per lane quarter sharing one stage
+  constexpr int kDequantSets = dequant_sets(CTAS, MX != 0), kEpiSets = epi_sets(CTAS);
   constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
   static_assert((kEpiWarp0 + 4 * kEpiSets) * 32 == kThreads, "the role split must use every warp");
   const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
@@ -512,7 +582,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
   // gate/up epilogue staging: 2 x (32 tokens x 64 features) bf16, 16-byte aligned
   uint16_t* epi_stage = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(Barriers) + 127) & ~size_t(127)));
-  constexpr bool kUseLut = CTAS == 1;
+  constexpr bool kUseLut = CTAS == 1 && !MX;
   uint32_t* lut = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(epi_stage) +
                                               (GATEUP ? kEpiStageBytes : kEpiStageDownBytes));
 
@@ -523,10 +593,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   if (tid == 0) {
     for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
-      mbar_init(smem_u32(&bars->w_empty[i]), 4 * kDequantSets);
+      mbar_init(smem_u32(&bars->w_empty[i]), MX ? 4 * kMxSplit : 4 * kDequantSets);   // fp8 form: only the owning team reads a stage
     }
     for (int i = 0; i < kMaxAStages; ++i) {
-      mbar_init(smem_u32(&bars->a_full[i]), kMerged ? 4 * CTAS + 1 : 4);
+      mbar_init(smem_u32(&bars->a_full[i]), kMerged ? 4 * CTAS + 1 : (MX ? 4 * kMxSplit : 4));
       mbar_init(smem_u32(&bars->stage_done[i]), 1);
     }
     for (int i = 0; i < kMaxBStages; ++i) mbar_init(smem_u32(&bars->b_full[i]), 1);
@@ -534,8 +604,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->sc_full[i]), 1);
       mbar_init(smem_u32(&bars->sc_empty[i]), 4 * kDequantSets);
     }
-    mbar_init(smem_u32(&bars->acc_full), 1);
-    mbar_init(smem_u32(&bars->acc_empty), 4 * kEpiSets * CTAS);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->acc_full[i]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[i]), 4 * kEpiSets * CTAS);
+    }
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -690,6 +762,23 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t bar = smem_u32(&bars->b_full[b.slot]);
           const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
           const int k0 = st * KS;
+          if (MX) {
+            // fp8 tokens: [128-K half][piece 1 rows, piece 2 rows][128 bytes]; a half that sticks
+            // out past K is zero-filled by the copy, and its bytes still count
+            const int n_half = min(2, (p.K - k0 + 127) / 128);
+            mbar_expect_tx(bar, tt.n_rows * 128 * n_half * 2);
+            for (int pc = 0; pc < 2; ++pc) {
+              for (int kh = 0; kh < n_half; ++kh) {
+                const uint32_t d = dst + kh * 2 * slice_bytes + pc * tt.n_rows * 128;
+                const int row = pc * p.piece_rows + tt.row0;
+                int r = 0;
+                for (; r + 64 <= tt.n_rows; r += 64) tma_load_2d(d + r * 128, &tmap_b64, k0 + kh * 128, row + r, bar);
+                for (; r < tt.n_rows; r += 16) tma_load_2d(d + r * 128, &tmap_b, k0 + kh * 128, row + r, bar);
+              }
+            }
+            b.advance(p.b_stages);
+            continue;
+          }
           const int n_slices = min(kPieces, (p.K - k0) / 64);
           mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
           for (int sl = 0; sl < n_slices; ++sl) {
@@ -716,7 +805,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       // needs (barrier addresses, tensor-memory column, token descriptor) is carried along and
       // bumped per stage instead of being recomputed from the slot index.
       const uint32_t ready0 = smem_u32(&bars->a_full[0]), done0 = smem_u32(&bars->stage_done[0]);
-      const uint32_t acc_full_bar = smem_u32(&bars->acc_full);
+      const uint32_t acc_full_bar = smem_u32(&bars->acc_full[0]);
       const uint32_t a0 = tmem_u + kAccCols;
       const uint64_t desc_first = make_b_desc(smem_u32(b_smem));
       const uint32_t desc_step = (uint32_t)p.b_stage_bytes >> 4, slice16 = (uint32_t)slice_bytes >> 4;
@@ -729,7 +818,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const int n_main = min(n32, kPairMainTok), n_ext = n32 - n_main;
         const uint32_t idesc = make_idesc(n_main, 256), idesc_ext = make_idesc(n_ext, 256);
         const uint32_t ext16 = (uint32_t)(n_main >> 1) * 8u;   // descriptor offset of the extension rows
-        if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
+        if (!mbar_wait(smem_u32(&bars->acc_empty[0]), acc_phase ^ 1u, abort_flag, 4)) break;
         tc_fence_after();
         for (int st = 0; st < n_stages; ++st) {
           if (!mbar_wait(ready, phase, abort_flag, 5)) {
@@ -772,10 +861,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
     }
     Ring a, b;
-    for (int item = unit; item < n_items && ok && !kMerged; item += n_units) {
+    int acc_it = 0;
+    for (int item = unit; item < n_items && ok && !kMerged; item += n_units, ++acc_it) {
       const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
-      const uint32_t idesc = make_idesc(n_rows_u);
-      if (!mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1u, abort_flag, 4)) break;
+      const uint32_t idesc = MX ? make_idesc_mx(2 * n_rows_u) : make_idesc(n_rows_u);
+      const int ab = acc_it % kAccBufs;
+      const uint32_t d_addr = tmem_u + ab * kAccCols;
+      if (!mbar_wait(smem_u32(&bars->acc_empty[ab]), (((uint32_t)(acc_it / kAccBufs)) & 1u) ^ 1u, abort_flag, 4)) break;
       tc_fence_after();
       for (int st = 0; st < n_stages; ++st) {
         const uint32_t bar = lane == 0 ? smem_u32(&bars->a_full[a.slot]) : smem_u32(&bars->b_full[b.slot]);
@@ -786,27 +878,39 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         tc_fence_after();
         if (elect_one()) {
-          const int n_slices = min(kPieces, (p.K - st * KS) / 64);
-          const uint32_t a_addr = tmem_u + kAccCols + a.slot * kACols;
+          const uint32_t a_addr = tmem_u + kSlot0 + a.slot * kACols;
           const uint64_t desc0 = make_b_desc(smem_u32(b_smem + b.slot * p.b_stage_bytes));
           const uint32_t slice16 = (uint32_t)slice_bytes >> 4;
+          if (MX) {
+            // K blocks of 32: the block's 8 columns of e5m2 weights, its scale-factor byte (four
+            // blocks share a group of four columns), and the block's 32 bytes of each token piece
+            const int n_kb = min(8, (p.K - st * KS) / 32);
 #pragma unroll
-          for (int sl = 0; sl < kPieces; ++sl) {
-            if (sl < n_slices) {
+            for (int kb = 0; kb < 8; ++kb) {
+              if (kb < n_kb)
+                tc_mma_mx(d_addr, a_addr + kb * 8, desc0 + (kb >> 2) * 2 * slice16 + (kb & 3) * 2,
+                          idesc | ((uint32_t)(kb & 3) << 29), a_addr + KS / 4 + (kb >> 2) * 4, tmem_u + kSfbCol,
+                          (st | kb) != 0 ? 1u : 0u);
+            }
+          } else {
+            const int n_slices = min(kPieces, (p.K - st * KS) / 64);
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                tc_mma_ts(tmem_u, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
-                          (st | sl | kk) != 0 ? 1u : 0u);
+            for (int sl = 0; sl < kPieces; ++sl) {
+              if (sl < n_slices) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                  tc_mma_ts(d_addr, a_addr + sl * 32 + kk * 8, desc0 + sl * slice16 + kk * 2, idesc,
+                            (st | sl | kk) != 0 ? 1u : 0u);
+              }
             }
           }
           tc_commit(smem_u32(&bars->stage_done[a.slot]));
-          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full));
+          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full[ab]));
         }
         __syncwarp();
         a.advance(kAStages);
         b.advance(p.b_stages);
       }
-      acc_phase ^= 1u;
     }
   } else if (warp >= 4 && warp < kEpiWarp0) {
     // ------------------------------ dequant --------------------------------
@@ -821,7 +925,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // the gate rows of eight features, lanes 8-15 the matching up rows, so a 16x256b read of
     // the accumulator hands one thread the gate and the up value of the same (feature, token).
     const int srow = GATEUP ? (((row >> 3) & 1) * 64 + (row >> 4) * 8 + (row & 7)) : row;   // row inside the staged tile
-    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols;
+    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + kSlot0;
+    if (MX && h == 0) {
+      // unit scale factors of the token operand (the tokens carry their scale to the epilogue):
+      // written once; the first stage's hand-over to the MMA issuer orders them before any MMA
+      const uint32_t one = 0x7F7F7F7Fu;
+      tc_st4(tmem_base + ((uint32_t)(q * 32) << 16) + kSfbCol, one, one, one, one);
+    }
     const uint32_t lut_lane = smem_u32(lut) + (uint32_t)lane * 4u;
     Ring w, a;
     uint32_t sc_it = 0;
@@ -840,7 +950,126 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         pending = -1;
       }
     };
-    for (int item = unit; item < n_items && ok; item += n_units) {
+    if (MX) {
+      // fp8 form. A team (one warp per tensor-memory lane quarter) takes every kTeams-th stage of
+      // this CTA's running stage sequence (items follow each other without a gap in it); a warp
+      // expands its 32 rows of the stage in two halves of 128 K, each with the scale factors of
+      // its four 32-element groups. A team never touches another team's stages: its ring
+      // positions advance by kTeams and a packed-weight slot is released by its team alone.
+      // (kMxSplit = 2 would let two warps of a quarter share a stage, one half each: measured, no
+      // faster - the expansion is bound by the integer pipe of the scheduler both warps sit on.)
+      constexpr int kSplit = kMxSplit;               // warps per lane quarter that share a stage (1 or 2)
+      constexpr int kTeams = kDequantSets / kSplit;
+      const int team = h / kSplit, half0 = h % kSplit;
+      // staged-tile rows whose scale factors this thread copies (tensor-memory rows 32 i + lane)
+      int sf_row[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int L = 32 * i + lane;
+        sf_row[i] = GATEUP ? (((L >> 3) & 1) * 64 + (L >> 4) * 8 + (L & 7)) : L;
+      }
+      int w_slot = team % p.w_stages, a_slot = team;
+      uint32_t w_phase = (uint32_t)(team / p.w_stages) & 1u, a_phase = 0;
+      int g_base = 0;                        // running index of the item's first stage
+      for (int item = unit; item < n_items && ok; item += n_units, g_base += n_kw) {
+        const int f = item_f(item);
+        const int rows_valid = f >= p.n_ftiles ? 0 : (GATEUP ? 128 : min(128, p.n_feat - f * 128));
+        const int sbuf = sc_it % p.scale_bufs;
+        if (!mbar_wait(smem_u32(&bars->sc_full[sbuf]), (sc_it / p.scale_bufs) & 1u, abort_flag, 7)) break;
+        const uint8_t* sc_tile = sc_smem + sbuf * p.scale_buf_bytes;
+        const uint8_t* sf_src[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sf_src[i] = sf_row[i] < rows_valid ? sc_tile + sf_row[i] * pitch : nullptr;
+        for (int kw = (team - g_base) & (kTeams - 1); kw < n_kw; kw += kTeams) {
+          if (!mbar_wait(smem_u32(&bars->w_full[w_slot]), w_phase, abort_flag, 8) ||
+              !mbar_wait(smem_u32(&bars->stage_done[a_slot]), a_phase ^ 1u, abort_flag, 9)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint8_t* my_row = w_smem + w_slot * kWStageBytes + (srow >> 6) * (kWStageBytes / 2) + (srow & 63) * 128;
+          const int n_pieces = min(kPieces, (p.K - kw * kWStageK) / 64);   // 64-K pieces in this stage (4, or fewer at the end of K)
+          const uint32_t slot_col = t_row + a_slot * kACols;
+#pragma unroll
+          for (int half = half0; half < 2; half += kSplit) {
+            if (2 * half >= n_pieces) break;
+            // Scale factors of my four 32-element groups: column 4 * half + i, byte b = scale of
+            // tensor-memory row 32 i + lane for group 4 * half + b; every lane quarter keeps a
+            // full copy. A scale byte of 0xFF means zero in this layer but NaN to the tensor
+            // core: such a group is rewritten as scale 1 with zeroed values (NaN where the value
+            // was inf or NaN, as inf * 0 is).
+            uint32_t sf[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              sf[i] = 0x7F7F7F7Fu;
+              if (sf_src[i] != nullptr) {
+                const uint16_t* sp = reinterpret_cast<const uint16_t*>(sf_src[i] + kw * 8 + half * 4);
+                sf[i] = (uint32_t)sp[0] | ((uint32_t)sp[1] << 16);
+              }
+            }
+            const uint32_t mx4 = __vmaxu4(__vmaxu4(sf[0], sf[1]), __vmaxu4(sf[2], sf[3]));
+            uint32_t ff = 0u;   // 0x80 in the byte of each of MY row's groups whose scale is 0xFF
+            if ((((mx4 & 0x7F7F7F7Fu) + 0x01010101u) & mx4 & 0x80808080u) != 0u) {
+              const uint32_t own = q == 0 ? sf[0] : q == 1 ? sf[1] : q == 2 ? sf[2] : sf[3];
+              ff = ((own & 0x7F7F7F7Fu) + 0x01010101u) & own & 0x80808080u;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) sf[i] ^= ((sf[i] & 0x7F7F7F7Fu) + 0x01010101u) & sf[i] & 0x80808080u;   // 0xFF -> 0x7F
+            }
+#pragma unroll
+            for (int pp = 0; pp < 2; ++pp) {
+              const int pc = 2 * half + pp;
+              if (pc < n_pieces) {
+                uint32_t v[16];
+                if (srow < rows_valid) {
+                  const uint4 p0 = *reinterpret_cast<const uint4*>(my_row + (((2 * pc) ^ (srow & 7)) << 4));
+                  const uint4 p1 = *reinterpret_cast<const uint4*>(my_row + (((2 * pc + 1) ^ (srow & 7)) << 4));
+                  expand8_e5m2(p0.x, v + 0);
+                  expand8_e5m2(p0.y, v + 2);
+                  expand8_e5m2(p0.z, v + 4);
+                  expand8_e5m2(p0.w, v + 6);
+                  expand8_e5m2(p1.x, v + 8);
+                  expand8_e5m2(p1.y, v + 10);
+                  expand8_e5m2(p1.z, v + 12);
+                  expand8_e5m2(p1.w, v + 14);
+                  if (ff != 0u) {
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {   // groups 2 pp + g of my four
+                      if ((ff >> (8 * (2 * pp + g) + 7)) & 1u) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                          const uint32_t x = v[8 * g + i];
+                          v[8 * g + i] = ((((x & 0x7C7C7C7Cu) + 0x04040404u) & 0x80808080u) >> 7) * 0x7Eu;
+                        }
+                      }
+                    }
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) v[i] = 0u;
+                }
+                tc_st16(slot_col + pc * 16, v);
+              }
+            }
+            tc_st4(slot_col + KS / 4 + 4 * half, sf[0], sf[1], sf[2], sf[3]);
+          }
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&bars->a_full[a_slot]));
+            mbar_arrive(smem_u32(&bars->w_empty[w_slot]));
+          }
+          w_slot += kTeams;
+          while (w_slot >= p.w_stages) { w_slot -= p.w_stages; w_phase ^= 1u; }
+          a_slot += kTeams;
+          if (a_slot >= kAStages) { a_slot -= kAStages; a_phase ^= 1u; }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->sc_empty[sbuf]));
+        ++sc_it;
+      }
+    }
+    for (int item = unit; item < n_items && ok && !MX; item += n_units) {
       const int f = item_f(item);
       const int rows_valid = f >= p.n_ftiles ? 0 : (GATEUP ? 128 : min(128, p.n_feat - f * 128));
       const int sbuf = sc_it % p.scale_bufs;
@@ -917,9 +1146,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int es = (warp - kEpiWarp0) >> 2;          // epilogue set
     const int etid = tid - kEpiWarp0 * 32;           // 0 .. 128 * kEpiSets - 1
     const int ltid = etid & 127;                     // thread inside the set = TMEM lane
-    uint32_t acc_phase = 0;
+    int acc_it = 0;
     int round = 0;   // gate/up staging buffer parity of this set, running over all items
-    for (int item = unit; item < n_items; item += n_units, acc_phase ^= 1u) {
+    for (int item = unit; item < n_items; item += n_units, ++acc_it) {
+      const int ab = acc_it % kAccBufs;
+      const uint32_t acc_phase = ((uint32_t)(acc_it / kAccBufs)) & 1u;
       const TokTile tt = p.tiles[item / n_fgroups];
       const int f = item_f(item);
       // per-token info of this item (previous item's readers are past the barrier below)
@@ -935,19 +1166,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           bars->tile_ref[j] = real ? reinterpret_cast<unsigned long long>(orow) : 0ull;
         }
         if (!GATEUP) bars->tile_w[j] = (real && p.topk_w != nullptr) ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
+        if (MX) bars->tile_s[j] = real ? p.tok_scale[tt.row0 + j] : 0.0f;
       }
       // The wait's outcome is shared by all epilogue warps before anyone acts on it: a warp that
       // gave up must not leave the others standing at a later named barrier.
-      const bool gave_up = !mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, 10, 256);
+      const bool gave_up = !mbar_wait(smem_u32(&bars->acc_full[ab]), acc_phase, abort_flag, 10, 256);
       if (named_bar_or(1, 128 * kEpiSets, gave_up)) break;
       tc_fence_after();
-      const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+      const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + ab * kAccCols;
       auto release_acc = [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          if (CTAS == 2 && !leader) mbar_arrive_cta(smem_u32(&bars->acc_empty), 0);
-          else mbar_arrive(smem_u32(&bars->acc_empty));
+          if (CTAS == 2 && !leader) mbar_arrive_cta(smem_u32(&bars->acc_empty[ab]), 0);
+          else mbar_arrive(smem_u32(&bars->acc_empty[ab]));
         }
       };
       if (f >= p.n_ftiles || es * 32 >= tt.n_rows || (!GATEUP && (p.n_feat & 3) != 0 && es != 0)) {
@@ -971,6 +1203,17 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           uint32_t va[16], vb[16];
           tc_ld_16x256b_x4(t_lane + c0, va);
           tc_ld_16x256b_x4(t_lane + (16u << 16) + c0, vb);
+          if (MX) {   // the second piece's partial products sit n_rows columns further on
+            uint32_t wa[16], wb[16];
+            tc_ld_16x256b_x4(t_lane + tt.n_rows + c0, wa);
+            tc_ld_16x256b_x4(t_lane + (16u << 16) + tt.n_rows + c0, wb);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              va[i] = __float_as_uint(__uint_as_float(va[i]) + __uint_as_float(wa[i]));
+              vb[i] = __float_as_uint(__uint_as_float(vb[i]) + __uint_as_float(wb[i]));
+            }
+          }
           tc_wait_ld();
           if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
           if (p.raw != nullptr) {   // stage split: pre-activation sums, gate columns then up columns
@@ -1000,8 +1243,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           for (int i = 0; i < 4; ++i) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const float g0 = __uint_as_float(va[4 * i + e]) + bg[0], u0 = __uint_as_float(va[4 * i + 2 + e]) + bu[0];
-              const float g1 = __uint_as_float(vb[4 * i + e]) + bg[1], u1 = __uint_as_float(vb[4 * i + 2 + e]) + bu[1];
+              // fp8 form: the sums are in units of the token's scale (a power of two: exact)
+              const float ts = MX ? bars->tile_s[c0 + 8 * i + tk + e] : 1.0f;
+              const float g0 = __uint_as_float(va[4 * i + e]) * ts + bg[0], u0 = __uint_as_float(va[4 * i + 2 + e]) * ts + bu[0];
+              const float g1 = __uint_as_float(vb[4 * i + e]) * ts + bg[1], u1 = __uint_as_float(vb[4 * i + 2 + e]) * ts + bu[1];
               uint16_t* d = stg + (8 * i + e) * kEpiPitch;
               if (!situ) {
                 d[0] = f32_to_bf16_bits(swiglu_fast(g0, u0, p.limit));
@@ -1044,6 +1289,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           for (int c0 = es * 32; c0 < tt.n_rows; c0 += 32 * kEpiSets) {
             uint32_t v[32];
             tc_ld32(t_lane + c0, v);
+            if (MX) {   // the second piece's partial products sit n_rows columns further on
+              uint32_t v2[32];
+              tc_ld32(t_lane + tt.n_rows + c0, v2);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+            }
             tc_wait_ld();
             if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
 #pragma unroll
@@ -1056,16 +1308,25 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
               for (int i = 0; i < 4; ++i) {
                 const int tl = (lane >> 3) + 4 * i;
                 const int t = c0 + half * 16 + tl;
-                if (p.raw != nullptr) {   // stage split: plain partial rows, no bias, no routing weight
-                  if (t < tt.n_rows && quad_ok)
-                    *reinterpret_cast<float4*>(p.raw + (size_t)(tt.row0 + t) * p.raw_ld + h0) =
-                        *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                if (p.raw != nullptr) {   // plain partial rows, no bias, no routing weight
+                  if (t < tt.n_rows && quad_ok) {
+                    float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                    if (MX) {
+                      const float ts = bars->tile_s[t];
+                      a.x *= ts; a.y *= ts; a.z *= ts; a.w *= ts;
+                    }
+                    *reinterpret_cast<float4*>(p.raw + (size_t)(tt.row0 + t) * p.raw_ld + h0) = a;
+                  }
                   continue;
                 }
                 float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
                 if (orow != nullptr && quad_ok) {
                   const float wgt = bars->tile_w[t];
-                  const float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                  float4 a = *reinterpret_cast<const float4*>(stage + tl * 32 + hq);
+                  if (MX) {
+                    const float ts = bars->tile_s[t];
+                    a.x *= ts; a.y *= ts; a.z *= ts; a.w *= ts;
+                  }
                   if (p.out_rows != nullptr)
                     red_add_v4_sys(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
                                    (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
@@ -1083,6 +1344,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           for (int c0 = 0; c0 < tt.n_rows; c0 += 32) {
             uint32_t v[32];
             tc_ld32(t_lane + c0, v);
+            if (MX) {
+              uint32_t v2[32];
+              tc_ld32(t_lane + tt.n_rows + c0, v2);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+            }
             tc_wait_ld();
             if (c0 + 32 >= tt.n_rows) release_acc();
 #pragma unroll 4
@@ -1090,7 +1358,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
               const int t = c0 + j;
               float* orow = t < tt.n_rows ? reinterpret_cast<float*>(bars->tile_ref[t]) : nullptr;
               if (orow != nullptr && row_ok)
-                atomicAdd(orow + hcol, (__uint_as_float(v[j]) + b) * bars->tile_w[t]);
+                atomicAdd(orow + hcol, (__uint_as_float(v[j]) * (MX ? bars->tile_s[t] : 1.0f) + b) * bars->tile_w[t]);
             }
           }
         }
@@ -1141,15 +1409,14 @@ __global__ void wait_timeout_probe_kernel(long long limit_clocks) {
 // Token tiles from expert_ids: a run of consecutive blocks with the same
 // non-negative expert becomes ceil(rows / max_tok) tiles of (almost) equal
 // size, each a multiple of 16 rows.
-__global__ void __launch_bounds__(1024)
-build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size, int max_tok,
-                   TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
-  __shared__ int scan[1024];
-  __shared__ int base;
+template <int NT>
+__device__ __forceinline__ void build_tiles_block(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size,
+                                                  int max_tok, TokTile* __restrict__ tiles, int* __restrict__ n_tiles,
+                                                  int max_tiles, int* scan /* [NT] shared */, int* base /* shared */) {
   const int tid = threadIdx.x;
-  if (tid == 0) base = 0;
+  if (tid == 0) *base = 0;
   __syncthreads();
-  for (int b0 = 0; b0 < n_blocks; b0 += 1024) {
+  for (int b0 = 0; b0 < n_blocks; b0 += NT) {
     const int b = b0 + tid;
     int e = -1, run_blocks = 0;
     if (b < n_blocks) {
@@ -1164,14 +1431,14 @@ build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int blo
     const int nt = (rows + max_tok - 1) / max_tok;
     scan[tid] = nt;
     __syncthreads();
-    for (int d = 1; d < 1024; d <<= 1) {
+    for (int d = 1; d < NT; d <<= 1) {
       const int v = tid >= d ? scan[tid - d] : 0;
       __syncthreads();
       scan[tid] += v;
       __syncthreads();
     }
     if (nt > 0) {
-      int at = base + scan[tid] - nt;
+      int at = *base + scan[tid] - nt;
       // equal split, rounded up to 16 rows
       const int per = (((rows + nt - 1) / nt) + 15) & ~15;
       int r = 0;
@@ -1182,10 +1449,18 @@ build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int blo
       }
     }
     __syncthreads();
-    if (tid == 0) base += scan[1023];
+    if (tid == 0) *base += scan[NT - 1];
     __syncthreads();
   }
-  if (tid == 0) *n_tiles = min(base, max_tiles);
+  if (tid == 0) *n_tiles = min(*base, max_tiles);
+}
+
+__global__ void __launch_bounds__(1024)
+build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int block_size, int max_tok,
+                   TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+  __shared__ int scan[1024];
+  __shared__ int base;
+  build_tiles_block<1024>(expert_ids, n_blocks, block_size, max_tok, tiles, n_tiles, max_tiles, scan, &base);
 }
 
 // A_sorted[r, :] = A[sorted_ids[r] / top_k, :] (or the row at A_rows[sorted_ids[r] / top_k]) for
@@ -1194,7 +1469,7 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint16_t* __restrict__ A, const uint16_t* const* __restrict__ A_rows,
                    const int32_t* __restrict__ sorted_ids,
                    const int32_t* __restrict__ expert_ids, int block_size, int EM, int N, int top_k,
-                   int H, uint16_t* __restrict__ dst) {
+                   int H, uint16_t* __restrict__ dst, int32_t* __restrict__ inv = nullptr) {
   const int vec_per_row = H / 8;  // 16-byte vectors
   const int rows_per_cta = 4;
   const int r0 = blockIdx.x * rows_per_cta;
@@ -1205,12 +1480,176 @@ gather_rows_kernel(const uint16_t* __restrict__ A, const uint16_t* const* __rest
     const int flat = sorted_ids[r];
     const bool real = flat >= 0 && flat < N;
     const int token = real ? flat / top_k : 0;
+    if (real && inv != nullptr && threadIdx.x == 0) inv[flat] = r;
     // a row address from A_rows may lie in another GPU's memory (peer load over NVLink)
     const uint4* src = reinterpret_cast<const uint4*>(
         A_rows != nullptr ? (real ? A_rows[token] : nullptr) : A + (size_t)token * H);
     uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * H);
     for (int i = threadIdx.x; i < vec_per_row; i += 256)
       d[i] = real ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Token rows of the fp8 form. Row r of the sorted order (gate/up: the activation row of token
+// sorted_ids[r] / top_k, or the row at src_rows[token]; down: row r of `src` itself) becomes two
+// e4m3 pieces and a scale: x = s * (p1 + p2), s = 2^(floor(log2 max|x|) - 7), p1 = e4m3(x / s)
+// rounded to nearest, p2 = e4m3(x / s - p1). |x / s| < 256, so p1 keeps the top four significant
+// bits and p2 the next four: exact for a bf16 value unless it lies more than 2^9 below the row's
+// largest (then p2 loses its lowest bits: an error below 2^-17 of the row's largest value).
+// inf and NaN become NaN in p1. Padding rows of used blocks are zero; unused blocks are skipped.
+// One warp per row, two passes over the row (largest magnitude, then the pieces). The gather
+// variant also does two small jobs of the layer's front end so that they cost no launch of their
+// own: the CTA after the last row CTA builds the token-tile list (tiles != nullptr), and every
+// real row records where its routed slot went (inv[flat] = r, when inv != nullptr).
+template <bool GATHER>
+__global__ void __launch_bounds__(128)
+split_rows_kernel(const uint16_t* __restrict__ src, const uint16_t* const* __restrict__ src_rows,
+                  const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
+                  int block_size, int EM, int N, int top_k, int K, uint8_t* __restrict__ p1,
+                  uint8_t* __restrict__ p2, float* __restrict__ tok_scale, int32_t* __restrict__ inv,
+                  int max_tok, TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+  if (GATHER && blockIdx.x * 4 >= EM) {   // the extra CTA
+    __shared__ int scan[128];
+    __shared__ int base;
+    if (tiles != nullptr)
+      build_tiles_block<128>(expert_ids, EM / block_size, block_size, max_tok, tiles, n_tiles, max_tiles, scan, &base);
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= EM) return;
+  if (expert_ids[r / block_size] < 0) return;   // never read by any tile
+  const int flat = sorted_ids[r];
+  const bool real = flat >= 0 && flat < N;
+  if (GATHER && real && inv != nullptr && lane == 0) inv[flat] = r;
+  const int n_vec = K / 8;
+  uint2* d1 = reinterpret_cast<uint2*>(p1 + (size_t)r * K);
+  uint2* d2 = reinterpret_cast<uint2*>(p2 + (size_t)r * K);
+  if (!real) {
+    for (int i = lane; i < n_vec; i += 32) d1[i] = d2[i] = make_uint2(0u, 0u);
+    if (lane == 0) tok_scale[r] = 1.0f;
+    return;
+  }
+  const uint4* row;
+  if (GATHER) {
+    const int token = flat / top_k;
+    row = reinterpret_cast<const uint4*>(src_rows != nullptr ? src_rows[token] : src + (size_t)token * K);
+  } else {
+    row = reinterpret_cast<const uint4*>(src + (size_t)r * K);
+  }
+  // pass 1: largest finite magnitude (bf16 bit patterns order like their magnitudes)
+  uint32_t mx = 0u;
+  for (int i = lane; i < n_vec; i += 32) {
+    const uint4 v = row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo = w[j] & 0x7FFFu, hi = (w[j] >> 16) & 0x7FFFu;
+      if (lo < 0x7F80u) mx = max(mx, lo);
+      if (hi < 0x7F80u) mx = max(mx, hi);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+  int e = (int)(mx >> 7) - 127;            // exponent of the largest magnitude
+  if (mx == 0u) e = 7;                      // all-zero row: scale 1
+  e = max(e, -119);                         // keep 2^(e - 7) a normal fp32
+  const float inv_s = __uint_as_float((uint32_t)(127 + 7 - e) << 23);
+  if (lane == 0) tok_scale[r] = __uint_as_float((uint32_t)(127 + e - 7) << 23);
+  // pass 2: the two pieces
+  for (int i = lane; i < n_vec; i += 32) {
+    const uint4 v = row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o1[2], o2[2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = make_float2(bf16_bits_to_f32(w[j] & 0xFFFFu) * inv_s, bf16_bits_to_f32(w[j] >> 16) * inv_s);
+      if (!isfinite(f.x)) f.x = __int_as_float(0x7FC00000);
+      if (!isfinite(f.y)) f.y = __int_as_float(0x7FC00000);
+      const uint32_t a = (uint32_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      const __half2_raw hb = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)a, __NV_E4M3);
+      const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hb));
+      const uint32_t b = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f.x - back.x, f.y - back.y), __NV_SATFINITE, __NV_E4M3);
+      if (j & 1) {
+        o1[j >> 1] |= a << 16;
+        o2[j >> 1] |= b << 16;
+      } else {
+        o1[j >> 1] = a;
+        o2[j >> 1] = b;
+      }
+    }
+    d1[i] = make_uint2(o1[0], o1[1]);
+    d2[i] = make_uint2(o2[0], o2[1]);
+  }
+}
+
+// Ordered combine: y[t, :] = bf16( sum over the token's routed slots, in ascending sorted-row
+// order - for one token that is ascending expert order, the order in which the CPU definition
+// adds (reference moe_fused.cpp:539-562) - of (partial[r, :] + b2[e, :]) * w ). No atomics: the
+// result does not depend on which CTA finished first, and the fp32 accumulator never travels
+// through memory. inv[flat] = sorted row of routed slot `flat`; an entry is trusted only if
+// sorted_ids[inv[flat]] == flat (slots that were not routed leave stale entries behind).
+constexpr int kMaxCombineSlots = 32;
+__global__ void __launch_bounds__(256)
+combine_rows_kernel(const float* __restrict__ partial, const float* __restrict__ b2, const float* __restrict__ topk_w,
+                    int w_sorted, const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
+                    const int32_t* __restrict__ inv, int block_size, int EM, int top_k, int H,
+                    uint16_t* __restrict__ y_bf16, float* __restrict__ out_f32) {
+  __shared__ int s_row[kMaxCombineSlots];
+  __shared__ int s_exp[kMaxCombineSlots];
+  __shared__ float s_w[kMaxCombineSlots];
+  __shared__ int s_n;
+  const int t = blockIdx.x;
+  if (threadIdx.x < 32) {
+    // lane j looks slot j up (three dependent loads, all slots at once); a valid slot's place in
+    // the order is the number of valid slots on smaller rows
+    const int j = threadIdx.x;
+    int r = -1, e = -1;
+    float w = 0.0f;
+    if (j < top_k) {
+      const int flat = t * top_k + j;
+      const int cand = inv[flat];
+      if (cand >= 0 && cand < EM && sorted_ids[cand] == flat) {
+        e = expert_ids[cand / block_size];
+        if (e >= 0) {
+          r = cand;
+          w = topk_w[w_sorted ? cand : flat];
+        }
+      }
+    }
+    const unsigned valid = __ballot_sync(0xFFFFFFFFu, r >= 0);
+    int rank = 0;
+    for (int o = 0; o < top_k; ++o) {
+      const int ro = __shfl_sync(0xFFFFFFFFu, r, o);
+      if (ro >= 0 && ro < r) ++rank;
+    }
+    if (r >= 0) {
+      s_row[rank] = r;
+      s_exp[rank] = e;
+      s_w[rank] = w;
+    }
+    if (j == 0) s_n = __popc(valid);
+  }
+  __syncthreads();
+  const int n = s_n;
+  for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < n; ++i) {
+      float4 v = *reinterpret_cast<const float4*>(partial + (size_t)s_row[i] * H + c);
+      if (b2 != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(b2 + (size_t)s_exp[i] * H + c);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      const float w = s_w[i];
+      acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+    }
+    if (out_f32 != nullptr) *reinterpret_cast<float4*>(out_f32 + (size_t)t * H + c) = acc;
+    if (y_bf16 != nullptr) {
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(acc.x) | ((uint32_t)f32_to_bf16_bits(acc.y) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(acc.z) | ((uint32_t)f32_to_bf16_bits(acc.w) << 16);
+      *reinterpret_cast<uint2*>(y_bf16 + (size_t)t * H + c) = o;
+    }
   }
 }
 
@@ -1275,20 +1714,43 @@ CUtensorMap make_map(const void* ptr, CUtensorMapDataType dt, int elem_bytes, ui
 
 int max_tok_tiles(int EM) { return EM / 16 + 1; }
 
+// gathered: [EM, hidden] bf16 rows, or - fp8 form - the two e4m3 pieces [2][EM, hidden] of the
+// same size; act8: the pieces of the activation rows [2][EM, ispp]; scales: one fp32 per row each.
+// ordered = the bf16-output form: + the inverse permutation [N] and the fp32 partial rows
+// [EM, hidden] of the down GEMM.
 struct WsLayout {
-  size_t tiles_off, count_off, gathered_off, total;
+  size_t tiles_off, count_off, gathered_off, act8_off, scale_x_off, scale_a_off, inv_off, partial_off, total;
 };
-WsLayout ws_layout(int EM, int hidden) {
+WsLayout ws_layout(int EM, int hidden, int ispp, bool ordered = false, int N = 0) {
   WsLayout l{};
   size_t off = 0;
   l.count_off = off;  off += 256;
   l.tiles_off = off;  off += (size_t)max_tok_tiles(EM) * sizeof(TokTile);
   off = (off + 1023) & ~size_t(1023);
   l.gathered_off = off;  off += (size_t)EM * hidden * sizeof(uint16_t);
+  l.act8_off = off;  off += (size_t)EM * ispp * sizeof(uint16_t);
+  l.scale_x_off = off;  off += (size_t)EM * sizeof(float);
+  l.scale_a_off = off;  off += (size_t)EM * sizeof(float);
+  off = (off + 1023) & ~size_t(1023);
+  if (ordered) {
+    l.inv_off = off;  off += (size_t)N * sizeof(int32_t);
+    off = (off + 1023) & ~size_t(1023);
+    l.partial_off = off;  off += (size_t)EM * hidden * sizeof(float);
+  }
   l.total = off;
   return l;
 }
 
+
+// Small token tiles (up to 64 rows) run the fp8 form; VK_MOE_SMALL=bf16 keeps them on the
+// bf16 table form (which also propagates an infinite activation as inf rather than NaN).
+bool small_fp8_mode() {
+  static const bool on = [] {
+    const char* e = std::getenv("VK_MOE_SMALL");
+    return e == nullptr || std::string(e) != "bf16";
+  }();
+  return on;
+}
 
 // Large token tiles run on CTA pairs; VK_MOE_PAIR=0 keeps every launch on single CTAs.
 bool pair_mode() {
@@ -1308,7 +1770,7 @@ bool pair_fits(const GemmParams& p, bool gateup) {
   return 227 * 1024 - fixed - scale_tile - tokens >= 2 * kWStageBytes;
 }
 
-template <bool GATEUP, int KS, int CTAS>
+template <bool GATEUP, int KS, int CTAS, int MX = 0>
 void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                     cudaStream_t stream) {
   // Shared memory: token stages (this CTA's rows x KS), scales (double-buffered when they fit),
@@ -1316,15 +1778,18 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   // 16 KB): the deeper it is, the more weight bytes are in flight, which is what a decode-size
   // batch is bound by.
   constexpr int kAccCols = acc_cols(KS, CTAS);
-  constexpr int kAStages = (kTmemCols - kAccCols) / (KS / 2);
+  constexpr int kAStages = MX ? (kTmemCols - 128 - 8) / (KS / 4 + 8) : (kTmemCols - kAccCols) / (KS / 2);
+  constexpr int kThreads = block_threads(CTAS, MX != 0);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : kEpiStageDownBytes) + 128 +
-                    (CTAS == 1 ? kLutBytes : 0);
+                    (CTAS == 1 && !MX ? kLutBytes : 0);
   // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
   p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
   // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot
-  int b_stages = CTAS == 2 ? kAStages : (kAStages < 4 ? kAStages : 4), scale_bufs = 2;
+  // (the fp8 form keeps three token slots and gives the room to the packed-weight ring, whose
+  // depth is what covers the HBM latency)
+  int b_stages = CTAS == 2 ? kAStages : (MX ? 3 : (kAStages < 4 ? kAStages : 4)), scale_bufs = 2;
   auto w_room = [&]() {
     return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
   };
@@ -1348,12 +1813,12 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   int dev = 0;
   VK_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !configured[dev].load()) {
-    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS>,
+    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     if (dev >= 0 && dev < 64) configured[dev].store(true);
   }
   if (CTAS == 1) {
-    moe_gemm_sm100_kernel<GATEUP, KS, CTAS><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+    moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
   } else {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(sm_count() & ~1));
@@ -1367,15 +1832,17 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    VK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_gemm_sm100_kernel<GATEUP, KS, CTAS>, tw, tb, tb64, p));
+    VK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX>, tw, tb, tb64, p));
   }
 }
 
 // Stage length and CTA grouping by the largest token tile of the launch (see the kernel's comment).
 template <bool GATEUP>
 void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
-                 bool use_pair, cudaStream_t stream) {
-  if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
+                 bool use_pair, cudaStream_t stream, bool mx = false) {
+  if (p.max_tok <= 32 && mx) launch_gemm_ks<GATEUP, 256, 1, 32>(tw, tb, tb64, p, stream);
+  else if (p.max_tok <= 64 && mx) launch_gemm_ks<GATEUP, 256, 1, 64>(tw, tb, tb64, p, stream);
+  else if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
   else if (use_pair) launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
   else launch_gemm_ks<GATEUP, 64, 1>(tw, tb, tb64, p, stream);
@@ -1383,7 +1850,8 @@ void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap
 
 }  // namespace
 
-size_t sm100_workspace_bytes(int EM, int hidden, int /*ispp*/) { return ws_layout(EM, hidden).total; }
+size_t sm100_workspace_bytes(int EM, int hidden, int ispp) { return ws_layout(EM, hidden, ispp).total; }
+size_t sm100_workspace_bytes_ordered(int EM, int hidden, int ispp, int N) { return ws_layout(EM, hidden, ispp, true, N).total; }
 // ---------------------------------------------------------------------------
 // optional per-kernel timing: CUDA events recorded around the two GEMM kernels
 // on the launch stream (no synchronisation while recording), summed on demand.
@@ -1508,18 +1976,23 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                       float swiglu_limit, int activation, float beta, float linear_beta,
                       const float* b13, const float* b2, int block_size, cudaStream_t stream,
-                      const RowPtrs* rows) {
+                      const RowPtrs* rows, uint16_t* y_bf16) {
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   const uint16_t* const* a_rows = rows ? rows->a_rows : nullptr;
   float* const* out_rows = rows ? rows->out_rows : nullptr;
   expects(aligned16(A) && aligned16(w13) && aligned16(w13_scale) && aligned16(w2) &&
               aligned16(w2_scale) && aligned16(act_scratch),
           "fused_moe_mxfp4: A, weights, scales and act_scratch must be 16-byte aligned");
-  const WsLayout l = ws_layout(EM, hidden);
+  // y_bf16 != nullptr: the down GEMM leaves plain partial rows and an ordered combine writes the
+  // bf16 result (no atomics, no fp32 output buffer to zero and convert)
+  const bool ordered = y_bf16 != nullptr;
+  const WsLayout l = ws_layout(EM, hidden, ispp, ordered, M * top_k);
   uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total, stream));
   TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
   int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);
   uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
+  int32_t* inv = ordered ? reinterpret_cast<int32_t*>(ws + l.inv_off) : nullptr;
+  float* partial = ordered ? reinterpret_cast<float*>(ws + l.partial_off) : nullptr;
 
   // The number of experts is not an argument of the layer; the tensor maps
   // cover the rows of every expert id that fits an int32 row index.
@@ -1527,43 +2000,74 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   const TileChoice choice = choose_tiles(M, top_k, EM, block_size, hidden, ispp);
   const int max_tok = choice.max_tok;
   const bool use_pair = choice.use_pair;
-  build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
-                                             n_tiles, max_tok_tiles(EM));
-  gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM,
-                                                       M * top_k, top_k, hidden, gathered);
+  const bool mx = max_tok <= 64 && small_fp8_mode();
+  // a small problem's tile list is built by an extra CTA of the row pre-pass (one launch less)
+  const bool tiles_in_split = mx && EM / block_size <= 1024;
+  if (!tiles_in_split)
+    build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
+                                               n_tiles, max_tok_tiles(EM));
+  uint8_t* x8 = reinterpret_cast<uint8_t*>(gathered);            // fp8 form: pieces of the token rows
+  uint8_t* a8 = ws + l.act8_off;                                 //           pieces of the activation rows
+  float* scale_x = reinterpret_cast<float*>(ws + l.scale_x_off);
+  float* scale_a = reinterpret_cast<float*>(ws + l.scale_a_off);
+  if (mx)
+    split_rows_kernel<true><<<(EM + 3) / 4 + 1, 128, 0, stream>>>(
+        A, a_rows, sorted_ids, expert_ids, block_size, EM, M * top_k, top_k, hidden, x8, x8 + (size_t)EM * hidden,
+        scale_x, inv, max_tok, tiles_in_split ? tiles : nullptr, n_tiles, max_tok_tiles(EM));
+  else
+    gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM,
+                                                         M * top_k, top_k, hidden, gathered, inv);
 
   GemmParams g{};
   g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles;
   g.N = M * top_k; g.top_k = top_k; g.w_sorted = w_sorted; g.activation = activation;
   g.limit = swiglu_limit; g.beta = beta; g.linear_beta = linear_beta; g.max_tok = max_tok;
+  g.piece_rows = EM;
+  // token operand: bf16 rows [EM, K], or the fp8 pieces as one byte matrix [2 * EM, K]
+  auto token_maps = [&](const void* rows, int K, CUtensorMap& tb, CUtensorMap& tb64) {
+    if (mx) {
+      tb = make_map(rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, 2 * (uint64_t)EM, (uint64_t)K, 128, 16);
+      tb64 = make_map(rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, 2 * (uint64_t)EM, (uint64_t)K, 128, 64);
+    } else {
+      tb = make_map(rows, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, EM, (uint64_t)K * 2, 64, 16);
+      tb64 = make_map(rows, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, EM, (uint64_t)K * 2, 64, 64);
+    }
+  };
 
   {  // gate/up
     GemmParams p = g;
-    p.w_scale = w13_scale; p.bias = b13; p.act = act_scratch;
+    p.w_scale = w13_scale; p.bias = b13; p.act = act_scratch; p.tok_scale = scale_x;
     p.K = hidden; p.n_feat = ispp; p.n_ftiles = ispp / 64;
     const CUtensorMap tw = make_map(w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, hidden / 2,
                                     w13_rows_cap, hidden / 2, 128, 64);
-    const CUtensorMap tb = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
-                                    (uint64_t)hidden * 2, 64, 16);
-    const CUtensorMap tb64 = make_map(gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hidden, EM,
-                                      (uint64_t)hidden * 2, 64, 64);
+    CUtensorMap tb, tb64;
+    token_maps(mx ? static_cast<const void*>(x8) : static_cast<const void*>(gathered), hidden, tb, tb64);
     timer_mark(0, stream);
-    launch_gemm<true>(tw, tb, tb64, p, use_pair, stream);
+    launch_gemm<true>(tw, tb, tb64, p, use_pair, stream, mx);
     timer_mark(1, stream);
   }
+  if (mx)
+    split_rows_kernel<false><<<(EM + 3) / 4, 128, 0, stream>>>(act_scratch, nullptr, sorted_ids, expert_ids, block_size,
+                                                               EM, M * top_k, top_k, ispp, a8, a8 + (size_t)EM * ispp,
+                                                               scale_a, nullptr, 0, nullptr, nullptr, 0);
   {  // down + combine
     GemmParams p = g;
-    p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out; p.out_rows = out_rows;
+    p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out; p.out_rows = out_rows; p.tok_scale = scale_a;
     p.K = ispp; p.n_feat = hidden; p.n_ftiles = (hidden + 127) / 128;
+    if (ordered) {
+      p.raw = partial;
+      p.raw_ld = hidden;
+    }
     const CUtensorMap tw = make_map(w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ispp / 2, w13_rows_cap,
                                     ispp / 2, 128, 64);
-    const CUtensorMap tb = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
-                                    (uint64_t)ispp * 2, 64, 16);
-    const CUtensorMap tb64 = make_map(act_scratch, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ispp, EM,
-                                      (uint64_t)ispp * 2, 64, 64);
-    launch_gemm<false>(tw, tb, tb64, p, use_pair, stream);
+    CUtensorMap tb, tb64;
+    token_maps(mx ? static_cast<const void*>(a8) : static_cast<const void*>(act_scratch), ispp, tb, tb64);
+    launch_gemm<false>(tw, tb, tb64, p, use_pair, stream, mx);
     timer_mark(2, stream);
   }
+  if (ordered)
+    combine_rows_kernel<<<M, 256, 0, stream>>>(partial, b2, topk_w, w_sorted, sorted_ids, expert_ids, inv, block_size, EM,
+                                               top_k, hidden, y_bf16, out);
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -1589,7 +2093,7 @@ void launch_moe_stage_gemm(int which, const uint16_t* rows_in, const uint8_t* w,
   expects(rows_in && w && w_scale && sorted_ids && expert_ids && raw, "moe stage: buffers must not be null");
   expects(aligned16(rows_in) && aligned16(w) && aligned16(w_scale) && aligned16(raw),
           "moe stage: buffers must be 16-byte aligned");
-  const WsLayout l = ws_layout(EM, which == 0 ? k_full : 64);
+  const WsLayout l = ws_layout(EM, which == 0 ? k_full : 64, 0);
   uint8_t* ws = static_cast<uint8_t*>(workspace_get(l.total, stream));
   TokTile* tiles = reinterpret_cast<TokTile*>(ws + l.tiles_off);
   int* n_tiles = reinterpret_cast<int*>(ws + l.count_off);

@@ -13,6 +13,7 @@
 #include <atomic>
 #include "common.cuh"
 #include "moe_fused.hpp"
+#include "moe_prep.cuh"
 
 namespace vkernels::kernels::cuda {
 
@@ -263,26 +264,38 @@ router_logits_warp_kernel(const uint16_t* __restrict__ x, const float* __restric
   if (lane == 0) logits[(size_t)t * E + e] = acc;
 }
 
-// ----------------------------- top-k ----------------------------------------
-// One warp per token. Expert e lives in lane e % 32, slot e / 32.
-constexpr int kMaxSlots = 32;  // E <= 1024
-
-struct Best {
-  float v;
-  int i;
-};
-// larger value wins; equal values: lower index wins
-__device__ __forceinline__ Best better(Best a, Best b) {
-  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
-}
-__device__ __forceinline__ Best warp_best(Best x) {
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    Best o{__shfl_xor_sync(0xFFFFFFFFu, x.v, d), __shfl_xor_sync(0xFFFFFFFFu, x.i, d)};
-    x = better(x, o);
+// Decode batches (a few thousand dot products at most): one CTA per (expert, token) dot, every
+// thread a handful of 16-byte loads in flight, so even a single token's 32 dots spread over 32
+// SMs and finish in one memory round trip instead of a warp's 90 dependent ones.
+__global__ void __launch_bounds__(256)
+router_logits_cta_kernel(const uint16_t* __restrict__ x, const float* __restrict__ wr,
+                         float* __restrict__ logits, int H, int E) {
+  __shared__ float part[8];
+  const int e = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
+  const uint2* xr = reinterpret_cast<const uint2*>(x + (size_t)t * H);     // 4 bf16
+  const float4* w = reinterpret_cast<const float4*>(wr + (size_t)e * H);   // 4 fp32
+  float acc = 0.0f;
+  for (int i = tid; i < H / 4; i += 256) {
+    const uint2 xv = xr[i];
+    const float4 wv = w[i];
+    acc = fmaf(bf16_bits_to_f32(xv.x & 0xFFFFu), wv.x, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.x >> 16), wv.y, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.y & 0xFFFFu), wv.z, acc);
+    acc = fmaf(bf16_bits_to_f32(xv.y >> 16), wv.w, acc);
   }
-  return x;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
+  if ((tid & 31) == 0) part[tid >> 5] = acc;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += part[i];   // fixed order: reproducible
+    logits[(size_t)t * E + e] = s;
+  }
 }
+
+using namespace prep;
 
 template <int SLOTS>
 __global__ void __launch_bounds__(128)
@@ -292,131 +305,49 @@ route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bi
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
-  const float NEG = -INFINITY;
-  float score[SLOTS], choice[SLOTS];
-  const float* l = logits + (size_t)t * E;
-  if (!sigmoid) {
-    float mx = NEG;
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-      const int e = s * 32 + lane;
-      score[s] = (e < E) ? l[e] : NEG;
-      mx = fmaxf(mx, score[s]);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
-    float den = 0.0f;
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-      const int e = s * 32 + lane;
-      score[s] = (e < E) ? expf(score[s] - mx) : 0.0f;
-      den += score[s];
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, d);
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-      const int e = s * 32 + lane;
-      score[s] = score[s] / den;
-      choice[s] = (e < E) ? (bias ? score[s] + bias[e] : score[s]) : NEG;
-    }
-  } else {
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-      const int e = s * 32 + lane;
-      if (e < E) {
-        score[s] = 1.0f / (1.0f + expf(-l[e]));
-        choice[s] = score[s] + (bias ? bias[e] : 0.0f);
-      } else {
-        score[s] = 0.0f;
-        choice[s] = NEG;
-      }
-    }
-    if (n_group > 1) {
-      const int gs = E / n_group;
-      // group score = sum of the two largest choices of the group
-      // (lane g keeps group g's score; n_group <= 32)
-      float my_gscore = NEG;
-      for (int g = 0; g < n_group; ++g) {
-        float a = NEG, b = NEG;
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-          const int e = s * 32 + lane;
-          if (e < E && e / gs == g) {
-            const float c = choice[s];
-            if (c > a) { b = a; a = c; } else if (c > b) { b = c; }
-          }
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-          const float oa = __shfl_xor_sync(0xFFFFFFFFu, a, d);
-          const float ob = __shfl_xor_sync(0xFFFFFFFFu, b, d);
-          // merge two (largest, second) pairs
-          const float na = fmaxf(a, oa);
-          const float nb = fmaxf(fminf(a, oa), fmaxf(b, ob));
-          a = na;
-          b = nb;
-        }
-        const float gsc = (gs >= 2) ? a + b : a;
-        if (lane == g) my_gscore = gsc;
-      }
-      unsigned keep = 0;  // bit g set = group g stays eligible
-      for (int r = 0; r < topk_group; ++r) {
-        // a taken group competes with index INT_MAX so it cannot win again
-        const bool open = lane < n_group && !((keep >> lane) & 1u);
-        Best x = warp_best(Best{open ? my_gscore : NEG, open ? lane : 0x7FFFFFFF});
-        if (x.i < n_group) keep |= 1u << x.i;
-      }
-#pragma unroll
-      for (int s = 0; s < SLOTS; ++s) {
-        const int e = s * 32 + lane;
-        if (e < E && !((keep >> (e / gs)) & 1u)) choice[s] = NEG;
-      }
-    }
-  }
-  // k rounds of arg-max with removal
   const int kk = k + n_shared;
-  float sum = 0.0f;
-  float my_w = 0.0f;  // lane r keeps the weight of pick r (k <= 32)
-  int my_id = 0;
-  unsigned used = 0;  // bit s set = this lane's slot s already picked
-  for (int r = 0; r < k; ++r) {
-    Best x{NEG, 0x7FFFFFFF};
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-      const int e = s * 32 + lane;
-      if (e < E && !((used >> s) & 1u)) x = better(x, Best{choice[s], e});
-    }
-    x = warp_best(x);
-    float sc = 0.0f;
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s)
-      if (s * 32 + lane == x.i) {
-        used |= 1u << s;
-        sc = score[s];
-      }
-    sc = __shfl_sync(0xFFFFFFFFu, sc, x.i & 31);
-    sum += sc;  // same order on every lane: pick 0, pick 1, ...
-    if (lane == r) {
-      my_w = sc;
-      my_id = x.i;
-    }
+  route_token<SLOTS>(logits + (size_t)t * E, bias, E, k, sigmoid, n_group, topk_group, renorm, scaling, n_shared, lane,
+                     ids + (size_t)t * kk, w + (size_t)t * kk);
+}
+
+// Small batches - at most 1024 routed slots, the decode regime: routing AND alignment in one CTA.
+// The warps route the tokens in turn (the ids stay in shared memory), then the CTA runs the
+// one-chunk stable counting sort of the alignment on them. A decode step is a chain of kernels of
+// a few microseconds each; this removes one launch and one global round trip from it. Outputs
+// are those of route_topk followed by moe_align_block_size (no expert map: the ids are the
+// layer's own expert indices, shared experts included).
+template <int SLOTS>
+__global__ void __launch_bounds__(kChunk)
+route_align_small_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k,
+                         int sigmoid, int n_group, int topk_group, int renorm, float scaling, int n_shared,
+                         int block_size, int max_EM, int32_t* __restrict__ ids, float* __restrict__ w,
+                         int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids,
+                         int32_t* __restrict__ out_em) {
+  extern __shared__ int smem[];
+  const int local_n = E + n_shared;
+  int* warp_hist = smem;                               // [(kWarps + 1) * local_n]
+  int* offset = warp_hist + (kWarps + 1) * local_n;    // [local_n]
+  int* s_tmp = offset + local_n;                       // [kChunk]
+  int32_t* s_ids = s_tmp + kChunk;                     // [kChunk]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kk = k + n_shared, N = T * kk;
+  for (int i = tid; i < max_EM; i += kChunk) sorted_ids[i] = N;
+  for (int i = tid; i < max_EM / block_size; i += kChunk) expert_ids[i] = -1;
+  for (int t = warp; t < T; t += kWarps)
+    route_token<SLOTS>(logits + (size_t)t * E, bias, E, k, sigmoid, n_group, topk_group, renorm, scaling, n_shared,
+                       lane, s_ids + t * kk, w + (size_t)t * kk);
+  __syncthreads();
+  int le = -1;
+  if (tid < N) {
+    le = s_ids[tid];
+    ids[tid] = le;
+    if (le < 0 || le >= local_n) le = -1;
   }
-  if (renorm) {
-    if (sigmoid) {
-      my_w = my_w / (sum + 1.0e-20f);
-    } else {
-      if (sum == 0.0f) sum = 1.0f;
-      my_w = my_w / sum;
-    }
-  }
-  my_w *= scaling;
-  if (lane < k) {
-    ids[(size_t)t * kk + lane] = my_id;
-    w[(size_t)t * kk + lane] = my_w;
-  } else if (lane < kk) {
-    ids[(size_t)t * kk + lane] = E + (lane - k);
-    w[(size_t)t * kk + lane] = 1.0f;
+  const int rank = chunk_rank(le, local_n, warp_hist);
+  scan_experts(warp_hist + kWarps * local_n, offset, local_n, block_size, max_EM, expert_ids, out_em, s_tmp);
+  if (le >= 0) {
+    const int pos = offset[le] + rank;
+    if (pos < max_EM) sorted_ids[pos] = tid;
   }
 }
 
@@ -428,7 +359,9 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
   if (T == 0) return;
   expects(x && wr && logits, "router_logits: null buffer");
   const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15u) == 0;
-  if (T <= 512 && H % 8 == 0 && aligned16) {   // 8- and 16-byte loads of whole rows
+  if ((long long)T * E <= 8192 && T <= 65535 && H % 8 == 0 && aligned16) {
+    router_logits_cta_kernel<<<dim3((unsigned)E, (unsigned)T), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, H, E);
+  } else if (T <= 512 && H % 8 == 0 && aligned16) {   // 8- and 16-byte loads of whole rows
     const long long pairs = (long long)T * E;
     router_logits_warp_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, wr, logits, T, H, E);
@@ -463,6 +396,45 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
     dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);
     router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, wr, logits, T, H, E);
   }
+  VK_CUDA_CHECK(cudaGetLastError());
+}
+
+void route_align_small(const float* logits, const float* bias, int T, int E, int k, int sigmoid, int n_group,
+                       int topk_group, int renorm, float scaling, int n_shared, int block_size, int max_EM,
+                       int32_t* ids, float* w, int32_t* sorted_ids, int32_t* expert_ids, int32_t* out_em,
+                       void* stream) {
+  expects(T > 0 && E > 0 && k > 0 && k <= E, "route_align_small: need T > 0 and 0 < k <= E");
+  expects(E <= 32 * kMaxSlots, "route_align_small: at most 1024 experts");
+  expects(n_shared >= 0 && k + n_shared <= 32, "route_align_small: k + n_shared must be at most 32");
+  expects((long long)T * (k + n_shared) <= kChunk, "route_align_small: at most 1024 routed slots");
+  expects(n_group >= 1 && n_group <= 32 && E % n_group == 0 && topk_group >= 1 && topk_group <= n_group,
+          "route_align_small: bad group configuration");
+  expects(n_group == 1 || sigmoid, "route_align_small: group limiting needs the sigmoid router");
+  expects(n_group == 1 || (E / n_group) * topk_group >= k, "route_align_small: kept groups hold fewer than k experts");
+  expects(block_size > 0 && max_EM > 0 && max_EM % block_size == 0,
+          "route_align_small: max_EM must be a positive multiple of block_size");
+  expects(logits && ids && w && sorted_ids && expert_ids && out_em, "route_align_small: null buffer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int local_n = E + n_shared;
+  const size_t smem = ((size_t)(kWarps + 1) * local_n + local_n + 2 * kChunk) * sizeof(int);
+  expects(smem <= 200 * 1024, "route_align_small: too many experts");
+  const int slots = (E + 31) / 32;
+#define VK_ROUTE_ALIGN(S)                                                                                     \
+  do {                                                                                                        \
+    if (smem > 48 * 1024)                                                                                     \
+      VK_CUDA_CHECK(cudaFuncSetAttribute(route_align_small_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem));                                                         \
+    route_align_small_kernel<S><<<1, kChunk, smem, s>>>(logits, bias, T, E, k, sigmoid, n_group, topk_group,  \
+                                                        renorm, scaling, n_shared, block_size, max_EM, ids, w, \
+                                                        sorted_ids, expert_ids, out_em);                      \
+  } while (0)
+  if (slots <= 1) VK_ROUTE_ALIGN(1);
+  else if (slots <= 2) VK_ROUTE_ALIGN(2);
+  else if (slots <= 4) VK_ROUTE_ALIGN(4);
+  else if (slots <= 8) VK_ROUTE_ALIGN(8);
+  else if (slots <= 16) VK_ROUTE_ALIGN(16);
+  else VK_ROUTE_ALIGN(32);
+#undef VK_ROUTE_ALIGN
   VK_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -115,10 +115,19 @@ class FusedMoEMxfp4:
     def _em_bound(self, T: int) -> int:
         return ops.align_em_bound(T, self.slots, self.n_experts_total, self.block_size)
 
+    # Batches up to this many tokens take the bf16-output form of the layer: ordered combine, no
+    # fp32 output buffer to zero and convert (two launches less per step, bit-reproducible).
+    ORDERED_COMBINE_TOKENS = 256
+
     def _workspace_bytes(self) -> int:
         T = self.max_tokens
-        return nr.load_library().vk_cuda_moe_workspace_bytes(self._em_bound(T), self.hidden, self.ispp,
-                                                             self.n_experts_total, T * self.slots)
+        lib = nr.load_library()
+        plain = lib.vk_cuda_moe_workspace_bytes(self._em_bound(T), self.hidden, self.ispp, self.n_experts_total,
+                                                T * self.slots)
+        Ts = min(T, self.ORDERED_COMBINE_TOKENS)
+        small = lib.vk_cuda_moe_workspace_bytes_bf16(self._em_bound(Ts), self.hidden, self.ispp, self.n_experts_total,
+                                                     Ts * self.slots)
+        return max(plain, small)
 
     def _reserve(self) -> None:
         """Everything a step needs, allocated once: the library scratch of the current stream and
@@ -171,15 +180,29 @@ class FusedMoEMxfp4:
         persistent buffer: consume it before the next call)."""
         return self.experts(x, topk_ids, topk_w, return_fp32=True)
 
-    def experts(self, x, topk_ids, topk_w, bufs=None, out_bf16=None, return_fp32=False):
-        """Alignment + the two grouped GEMMs for given routing; returns bf16 [T, hidden]."""
+    def experts(self, x, topk_ids, topk_w, bufs=None, out_bf16=None, return_fp32=False, aligned=None):
+        """Alignment + the two grouped GEMMs for given routing; returns bf16 [T, hidden].
+        ``aligned`` = (sorted_ids, expert_ids) skips the alignment (the fused small-batch router
+        has already produced it)."""
         T = x.shape[0]
         bufs = bufs or self._buffers(T)
         em = self._em_bound(T)
-        with _region("moe:apply.gpu_align"):
-            sids, eids, _ = ops.moe_align_block_size(
-                topk_ids, self.n_experts_total, self.block_size, max_EM=em,
-                out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
+        if aligned is not None:
+            sids, eids = aligned
+        else:
+            with _region("moe:apply.gpu_align"):
+                sids, eids, _ = ops.moe_align_block_size(
+                    topk_ids, self.n_experts_total, self.block_size, max_EM=em,
+                    out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
+        if not return_fp32 and T <= self.ORDERED_COMBINE_TOKENS:
+            y = bufs["y"].view(T, self.hidden) if out_bf16 is None else out_bf16
+            with _region("moe:apply.launch"):
+                ops.fused_moe_mxfp4_bf16_into(y, bufs["act"], x, self.w13, self.w13_scale, self.w2, self.w2_scale,
+                                              topk_w.reshape(-1), sids, eids, top_k=topk_ids.shape[1],
+                                              block_size=self.block_size, swiglu_limit=self.swiglu_limit,
+                                              activation=self.activation, beta=self.beta,
+                                              linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+            return y
         out = bufs["out"].view(T, self.hidden)
         with _region("moe:apply.launch"):
             out.zero_()
@@ -216,6 +239,19 @@ class FusedMoEMxfp4:
         """route -> align -> gate/up -> down+combine, all on the current stream."""
         ops.require(x.dim() == 2 and x.shape[1] == self.hidden, "x must be [T, hidden]")
         bufs = self._buffers(x.shape[0])
+        T = x.shape[0]
+        if T * self.slots <= 1024 and (logits is not None or self.router_weight is not None):
+            # decode-size batch: router top-k and alignment in one kernel
+            with _region("moe:apply.route"):
+                if logits is None:
+                    logits = ops.router_logits(x, self.router_weight, out=bufs["logits"].view(T, self.n_router))
+                ids, w, sids, eids, _ = ops.route_align_small(
+                    logits, self.top_k, block_size=self.block_size, bias=self.router_bias,
+                    sigmoid=self.routing == "sigmoid_group", n_group=self.n_group, topk_group=self.topk_group,
+                    renorm=self.renorm, scaling=self.scaling, n_shared=self.n_shared, max_EM=self._em_bound(T),
+                    out=(bufs["ids"].view(T, self.slots), bufs["w"].view(T, self.slots), bufs["sids"], bufs["eids"],
+                         bufs["out_em"]))
+            return self.experts(x, ids, w, bufs, out_bf16=out_bf16, aligned=(sids, eids))
         with _region("moe:apply.route"):
             ids, w = self.route(x, bufs, logits=logits)
         return self.experts(x, ids, w, bufs, out_bf16=out_bf16)

@@ -117,6 +117,39 @@ def route_topk(logits: torch.Tensor, top_k: int, *, bias: torch.Tensor | None = 
     return ids, w
 
 
+def route_align_small(logits: torch.Tensor, top_k: int, *, block_size: int = 16, bias: torch.Tensor | None = None,
+                      sigmoid: bool = False, n_group: int = 1, topk_group: int = 1, renorm: bool = True,
+                      scaling: float = 1.0, n_shared: int = 0, max_EM: int | None = None, out=None):
+    """``route_topk`` and ``moe_align_block_size`` as ONE kernel for at most 1024 routed slots
+    (``T * (top_k + n_shared)``). Returns ``(ids, weights, sorted_ids, expert_ids, out_em)``;
+    ``out`` may pass these five tensors preallocated."""
+    require(logits.dtype == torch.float32 and logits.dim() == 2, "logits must be fp32 [T, E]")
+    same_gpu_contiguous(logits, *([bias] if bias is not None else []))
+    T, E = logits.shape
+    kk = top_k + n_shared
+    require(0 < T * kk <= 1024, "route_align_small takes 1..1024 routed slots")
+    if max_EM is None:
+        max_EM = align_em_bound(T, kk, E + n_shared, block_size)
+    dev = logits.device
+    if out is None:
+        ids = torch.empty((T, kk), dtype=torch.int32, device=dev)
+        w = torch.empty((T, kk), dtype=torch.float32, device=dev)
+        sorted_ids = torch.empty(max_EM, dtype=torch.int32, device=dev)
+        expert_ids = torch.empty(max_EM // block_size, dtype=torch.int32, device=dev)
+        out_em = torch.empty(1, dtype=torch.int32, device=dev)
+    else:
+        ids, w, sorted_ids, expert_ids, out_em = out
+        require(sorted_ids.numel() >= max_EM and expert_ids.numel() >= max_EM // block_size,
+                "preallocated alignment buffers are too small")
+    with torch.cuda.device(dev):
+        rc = nr.load_library().vk_cuda_moe_route_align_small(
+            _ptr(logits), _ptr(bias), T, E, top_k, int(sigmoid), n_group, topk_group, int(renorm), float(scaling),
+            n_shared, block_size, max_EM, _ptr(ids), _ptr(w), _ptr(sorted_ids), _ptr(expert_ids), _ptr(out_em),
+            _stream(logits))
+    nr.check(rc, "route_align_small")
+    return ids, w, sorted_ids[:max_EM], expert_ids[: max_EM // block_size], out_em
+
+
 def reset_kernel_status() -> None:
     """Synchronise and clear the status word of the current device."""
     nr.check(nr.load_library().vk_cuda_moe_reset_kernel_status(), "reset_kernel_status")
@@ -205,6 +238,31 @@ def fused_moe_mxfp4_into(out_fp32, act_scratch, hidden_states, w13, w13_scale, w
                 _stream(hidden_states))
             nr.check(lib.vk_last_error_code(), "fused_moe_mxfp4")
     return out_fp32
+
+
+def fused_moe_mxfp4_bf16_into(y_bf16, act_scratch, hidden_states, w13, w13_scale, w2, w2_scale, topk_weights,
+                              sorted_ids, expert_ids, *, top_k: int, block_size: int = 16, swiglu_limit: float = 0.0,
+                              activation: int = SWIGLU, beta: float = 4.0, linear_beta: float = 25.0, b13=None, b2=None):
+    """The layer with a bf16 result written by an ordered, atomic-free combine (each token's expert
+    contributions added in ascending expert order): ``y_bf16`` [M, hidden] is overwritten, nothing
+    needs zeroing or converting. Everything is caller-owned; the library scratch of the current
+    stream must have been reserved at ``vk_cuda_moe_workspace_bytes_bf16`` (the layer object does)."""
+    M, hidden, ispp, _ = _check_layer_shapes(hidden_states, w13, w13_scale, w2, w2_scale, b13, b2)
+    same_gpu_contiguous(hidden_states, w13, w13_scale, w2, w2_scale, topk_weights, sorted_ids, expert_ids, y_bf16,
+                        act_scratch, *[t for t in (b13, b2) if t is not None])
+    EM = sorted_ids.numel()
+    require(EM % block_size == 0 and expert_ids.numel() * block_size >= EM, "sorted_ids / expert_ids do not match block_size")
+    require(y_bf16.dtype == torch.bfloat16 and y_bf16.numel() >= M * hidden, "y must be bf16 [M, hidden]")
+    require(act_scratch.dtype == torch.bfloat16 and act_scratch.numel() >= EM * ispp, "act_scratch must be bf16 [EM, ispp]")
+    require(topk_weights.dtype == torch.float32 and topk_weights.numel() >= M * top_k, "topk_weights too small")
+    with torch.cuda.device(hidden_states.device):
+        rc = nr.load_library().vk_cuda_fused_moe_mxfp4_bf16(
+            _ptr(hidden_states), _ptr(w13), _ptr(w13_scale), _ptr(w2), _ptr(w2_scale), _ptr(topk_weights),
+            _ptr(act_scratch), _ptr(y_bf16), M, hidden, ispp, top_k, _ptr(sorted_ids), _ptr(expert_ids), EM,
+            float(swiglu_limit), int(activation), float(beta), float(linear_beta), _ptr(b13), _ptr(b2), block_size,
+            _stream(hidden_states))
+    nr.check(rc, "fused_moe_mxfp4_bf16")
+    return y_bf16
 
 
 def fused_moe_mxfp4_rows_into(act_scratch, a_rows, out_rows, w13, w13_scale, w2, w2_scale, topk_weights,
