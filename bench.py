@@ -209,7 +209,7 @@ def workload_config(cfg, T, n_gpus):
 # checks outside the timed region: the layer's output and routing against the CPU oracle
 # ------------------------------------------------------------------------------------------------
 
-def oracle_parity(cfg, A, y, ids, tw, weights, n_tokens, seed, logits=None, router=None):
+def oracle_parity(cfg, A, y, ids, tw, weights, n_tokens, seed, logits=None, router=None, threads=None):
     """Compares `n_tokens` seeded rows of one rank's result with the CPU oracle run on the SAME
     routing (ids / weights as the GPU produced them), and the routing itself with the CPU routing
     restatement on tokens whose decisive score gap exceeds fp32 reassociation noise.
@@ -232,7 +232,7 @@ def oracle_parity(cfg, A, y, ids, tw, weights, n_tokens, seed, logits=None, rout
     sel = torch.from_numpy(touched.astype(np.int64)).to(A.device)
     wn = {k: v.index_select(0, sel).cpu().numpy() for k, v in weights.items()}
     Au = A.index_select(0, tok_t).cpu().view(torch.int16).numpy().view(np.uint16)
-    oracle.set_num_threads(os.cpu_count() or 1)
+    oracle.set_num_threads(threads or os.cpu_count() or 1)
     ref = oracle.moe_layer(Au, wn["w13"], wn["w13_scale"], wn["w2"], wn["w2_scale"], remap[ids_s], tw_s,
                            num_experts=int(touched.size), swiglu_limit=cfg.swiglu_limit)
     got = y.index_select(0, tok_t).float().cpu().numpy()
@@ -405,17 +405,36 @@ def run_single_gpu(args, cfg, T):
     xh = A.cpu().pin_memory()
     yh = torch.empty((T, cfg.H), dtype=torch.bfloat16).pin_memory()
     if logits is None and not args.skip_parity:
+        # serial: copy in, layer, copy out, wait - one step at a time
         e2e_step = lambda: layer.forward_host(xh, yh)
         for _ in range(args.warmup):
             e2e_step()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             e2e_step()
+        serial_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        # pipelined: the same three things per step, with the copies of neighbouring steps
+        # overlapping the layer (two pinned input and two pinned output batches in rotation)
+        from vkernels_b200.experts import HostPipeline
+
+        pipe = HostPipeline(layer, T)
+        xhs = [xh, xh.clone().pin_memory()]
+        yhs = [yh, torch.empty_like(yh).pin_memory()]
+        for i in range(args.warmup):
+            pipe.submit(xhs[i & 1], yhs[i & 1])
+        pipe.drain()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            pipe.submit(xhs[i & 1], yhs[i & 1])
+        pipe.drain()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        yh = yhs[(args.steps - 1) & 1]
         e2e_dev = yh.to(dev)
         e2e_par = oracle_parity(cfg, A, e2e_dev, ids0, tw0, w, min(args.parity_tokens, 32), cfg.seed + 1)
         e2e = {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.H * 2,
-               "d2h_bytes_per_step": T * cfg.H * 2, "ms_per_step": e2e_ms,
+               "d2h_bytes_per_step": T * cfg.H * 2, "ms_per_step": e2e_ms, "ms_per_step_serial": serial_ms,
+               "how": "HostPipeline: every step copies its batch in from pinned memory and its result out; the copies "
+                      "of neighbouring steps overlap the layer on separate streams",
                "parity": {k: e2e_par[k] for k in ("tokens", "max_abs", "rel_l2", "ok")}}
         if not e2e_par["ok"]:
             print(json.dumps({"error": "end-to-end output differs from the CPU oracle", "parity": e2e_par}), flush=True)
@@ -459,6 +478,12 @@ def run_multi_gpu(args, cfg, T):
     sl = slice(rank * T_local, (rank + 1) * T_local)
     A = syn.make_activations(cfg, T_global, backend="torch", device=dev, seed=cfg.seed)[sl].contiguous()
     logits = syn.make_zipf_logits(cfg, T_global, device=dev)[sl].contiguous() if cfg.zipf_alpha else None
+    if layer._peer is not None:
+        # inputs resident in HBM means: resident in the rank's registered activation buffer, which the
+        # owners of the experts read in place
+        A_in = layer.input_buffer(T_local)
+        A_in.copy_(A)
+        A = A_in
     step = lambda: layer(A, logits=logits)
     barrier = lambda: dist.barrier()
 
@@ -472,8 +497,10 @@ def run_multi_gpu(args, cfg, T):
         ids0 = torch.cat([ids0, torch.full((T_local, 1), cfg.E, dtype=torch.int32, device=dev)], 1)
         tw0 = torch.cat([tw0, torch.ones((T_local, 1), dtype=torch.float32, device=dev)], 1)
     full_w = syn.make_expert_weights(cfg, backend="torch", device=dev)
-    par = oracle_parity(cfg, A, y0, ids0.contiguous(), tw0.contiguous(), full_w, args.parity_tokens, cfg.seed + rank,
-                        logits=logits, router=syn.make_router(cfg, device=dev))
+    # (the ranks share the host's cores: each takes its share of the threads and a smaller sample)
+    par = oracle_parity(cfg, A, y0, ids0.contiguous(), tw0.contiguous(), full_w, min(args.parity_tokens, max(8, 64 // world)),
+                        cfg.seed + rank, logits=logits, router=syn.make_router(cfg, device=dev),
+                        threads=max(1, (os.cpu_count() or 1) // world))
     del full_w
     torch.cuda.empty_cache()
     agg = torch.tensor([par["max_abs"], par["rel_l2"], 0.0 if par["ok"] else 1.0,
@@ -533,7 +560,7 @@ def run_multi_gpu(args, cfg, T):
     # layer and reads its output rows back; wall clock between barriers, max over ranks
     xh = A.cpu().pin_memory()
     yh = torch.empty((T_local, cfg.H), dtype=torch.bfloat16).pin_memory()
-    xd = torch.empty_like(A)
+    xd = layer.input_buffer(T_local) if layer._peer is not None else torch.empty_like(A)
 
     def e2e_step():
         xd.copy_(xh, non_blocking=True)

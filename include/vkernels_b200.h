@@ -297,15 +297,35 @@ int vk_cuda_moe_ep_unpack_meta(const int32_t* meta, int R, int slots, const int3
  * count array (world int32). pack: writes this rank's records for d into segment `rank` of d's
  * area and then its count into count_bases[d][rank] (cursor [world] zeroed by the caller).
  * unpack: over all world*cap record slots of the local area; slots past recv_counts[s] become
- * "not routed" rows (ids -1, w 0). A cross-rank barrier belongs between the two. */
+ * "not routed" rows (ids -1, w 0); out_rows[r] = out_bases[s] + token * out_rows_per_token * H * 4
+ * (1 for the reduction form, slots for the slot-store form below). pack also resets its cursor to
+ * zero after publishing the counts. A cross-rank barrier belongs between the two. */
 int vk_cuda_moe_ep_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int T, int k,
                                   int n_shared, int world, int rank, const int32_t* expert_begin,
                                   int32_t* cursor, const uint64_t* meta_bases,
                                   const uint64_t* count_bases, int cap, void* stream);
 int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
                                     int slots, const uint64_t* x_bases, const uint64_t* out_bases,
-                                    int H, int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
-                                    void* stream);
+                                    int H, int out_rows_per_token, int32_t* ids, float* w, uint64_t* a_rows,
+                                    uint64_t* out_rows, void* stream);
+/* Slot-store form of the combine: vk_cuda_fused_moe_mxfp4_rows_store is
+ * vk_cuda_fused_moe_mxfp4_rows with out_blocks[m] = address of a [top_k, hidden] fp32 block of
+ * token m (in its home rank's memory); the row of slot j - act @ w2^T + b2, NOT weighted - is
+ * written to row j with plain 16-byte stores instead of being added with reductions. After a
+ * cross-rank barrier the home rank runs vk_cuda_moe_ep_combine_slots: y[t,:] = bf16(sum over the
+ * slots j in ascending global expert id ids[t,j] of w[t,j] * part[t,j,:]); slots with an id
+ * outside [0, n_experts) are skipped; either output may be NULL. No atomics: the result is
+ * bit-reproducible and adds in the single-rank oracle's order (moe_fused.cpp:539-562). */
+int vk_cuda_fused_moe_mxfp4_rows_store(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                                       const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                                       uint16_t* act_scratch, const uint64_t* out_blocks, int M, int hidden,
+                                       int ispp, int top_k, const int32_t* sorted_ids,
+                                       const int32_t* expert_ids, int EM, float swiglu_limit, int activation,
+                                       float beta, float linear_beta, const float* b13, const float* b2,
+                                       int block_size, void* stream);
+int vk_cuda_moe_ep_combine_slots(const float* part, const int32_t* ids, const float* w, int T, int k, int n_experts,
+                                 int H, uint16_t* y_bf16, float* out_f32, void* stream);
+
 /* Cross-rank barrier of the peer-memory form, run as a kernel on `stream`: flag_bases[d] is the
  * address, in this process, of rank d's flag array ([8 slots][world] int32, zero at start, in
  * memory every rank can address). The kernel publishes `epoch` into entry [slot][rank] of every

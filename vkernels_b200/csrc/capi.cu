@@ -44,9 +44,11 @@ void ep_launch_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int 
                               int cap, cudaStream_t stream);
 void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
                                 int slots, const unsigned long long* x_bases,
-                                const unsigned long long* out_bases, int H, int32_t* ids, float* w,
-                                unsigned long long* a_rows, unsigned long long* out_rows,
+                                const unsigned long long* out_bases, int H, int out_rows_per_token, int32_t* ids,
+                                float* w, unsigned long long* a_rows, unsigned long long* out_rows,
                                 cudaStream_t stream);
+void ep_launch_combine_slots(const float* part, const int32_t* ids, const float* w, int T, int k, int n_experts, int H,
+                             uint16_t* y_bf16, float* out_f32, cudaStream_t stream);
 }  // namespace vkernels::kernels::cuda
 
 enum { VK_OK = 0, VK_ERROR_INVALID_ARGUMENT = 1, VK_ERROR_OUT_OF_RANGE = 2,
@@ -364,12 +366,12 @@ int vk_cuda_moe_ep_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, 
 
 int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
                                     int slots, const uint64_t* x_bases, const uint64_t* out_bases,
-                                    int H, int32_t* ids, float* w, uint64_t* a_rows, uint64_t* out_rows,
-                                    void* stream) {
+                                    int H, int out_rows_per_token, int32_t* ids, float* w, uint64_t* a_rows,
+                                    uint64_t* out_rows, void* stream) {
   VK_TRY
   vkc::ep_launch_unpack_meta_peer(meta, recv_counts, world, cap, slots,
                                   reinterpret_cast<const unsigned long long*>(x_bases),
-                                  reinterpret_cast<const unsigned long long*>(out_bases), H, ids, w,
+                                  reinterpret_cast<const unsigned long long*>(out_bases), H, out_rows_per_token, ids, w,
                                   reinterpret_cast<unsigned long long*>(a_rows),
                                   reinterpret_cast<unsigned long long*>(out_rows),
                                   static_cast<cudaStream_t>(stream));
@@ -396,6 +398,28 @@ int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, con
                             topk_w, act_scratch, reinterpret_cast<float* const*>(out_rows), M, hidden,
                             ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta,
                             linear_beta, b13, b2, block_size, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_fused_moe_mxfp4_rows_store(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
+                                       const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
+                                       uint16_t* act_scratch, const uint64_t* out_blocks, int M, int hidden,
+                                       int ispp, int top_k, const int32_t* sorted_ids,
+                                       const int32_t* expert_ids, int EM, float swiglu_limit, int activation,
+                                       float beta, float linear_beta, const float* b13, const float* b2,
+                                       int block_size, void* stream) {
+  VK_TRY
+  vkc::fused_moe_mxfp4_rows(reinterpret_cast<const uint16_t* const*>(a_rows), w13, w13_scale, w2, w2_scale,
+                            topk_w, act_scratch, reinterpret_cast<float* const*>(out_blocks), M, hidden,
+                            ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta,
+                            linear_beta, b13, b2, block_size, stream, true);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
+int vk_cuda_moe_ep_combine_slots(const float* part, const int32_t* ids, const float* w, int T, int k, int n_experts,
+                                 int H, uint16_t* y_bf16, float* out_f32, void* stream) {
+  VK_TRY
+  vkc::ep_launch_combine_slots(part, ids, w, T, k, n_experts, H, y_bf16, out_f32, static_cast<cudaStream_t>(stream));
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 

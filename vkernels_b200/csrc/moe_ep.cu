@@ -214,17 +214,20 @@ ep_pack_meta_peer_kernel(const int32_t* __restrict__ topk_ids, const float* __re
   }
 }
 
-__global__ void ep_publish_counts_kernel(const int32_t* __restrict__ cursor,
+__global__ void ep_publish_counts_kernel(int32_t* __restrict__ cursor,
                                          const unsigned long long* __restrict__ count_bases, int world,
                                          int rank) {
   const int d = threadIdx.x;
-  if (d < world) reinterpret_cast<int32_t*>(count_bases[d])[rank] = cursor[d];
+  if (d < world) {
+    reinterpret_cast<int32_t*>(count_bases[d])[rank] = cursor[d];
+    cursor[d] = 0;   // ready for the next step: the caller zeroes it only once
+  }
 }
 
 __global__ void __launch_bounds__(256)
 ep_unpack_meta_peer_kernel(const int32_t* __restrict__ meta, const int32_t* __restrict__ recv_counts,
                            int world, int cap, int slots, const unsigned long long* __restrict__ x_bases,
-                           const unsigned long long* __restrict__ out_bases, int H,
+                           const unsigned long long* __restrict__ out_bases, int H, int out_rows_per_token,
                            int32_t* __restrict__ ids, float* __restrict__ w,
                            unsigned long long* __restrict__ a_rows, unsigned long long* __restrict__ out_rows) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -234,10 +237,64 @@ ep_unpack_meta_peer_kernel(const int32_t* __restrict__ meta, const int32_t* __re
   const int32_t* m = meta + (size_t)r * (1 + 2 * slots);
   const unsigned long long tok = valid ? (unsigned long long)m[0] : 0ull;
   a_rows[r] = x_bases[src] + tok * (unsigned long long)H * sizeof(uint16_t);
-  out_rows[r] = out_bases[src] + tok * (unsigned long long)H * sizeof(float);
+  out_rows[r] = out_bases[src] + tok * (unsigned long long)out_rows_per_token * H * sizeof(float);
   for (int j = 0; j < slots; ++j) {
     ids[(size_t)r * slots + j] = valid ? m[1 + j] : -1;
     w[(size_t)r * slots + j] = valid ? __int_as_float(m[1 + slots + j]) : 0.0f;
+  }
+}
+
+// Home-rank combine of the slot-store form: part[t, j, :] holds the unweighted result row of
+// token t's slot j, stored there by whichever rank owns that expert. y[t, :] = bf16( sum over the
+// slots in ascending GLOBAL expert id - the order in which the single-rank CPU definition adds
+// (reference moe_fused.cpp:539-562), and with contiguous expert ranges also ascending rank order
+// - of w[t, j] * part[t, j, :] ). No atomics anywhere: the result is bit-reproducible. Slots whose
+// id is outside [0, n_experts) were never written and are skipped.
+__global__ void __launch_bounds__(256)
+ep_combine_slots_kernel(const float* __restrict__ part, const int32_t* __restrict__ ids, const float* __restrict__ w,
+                        int k, int n_experts, int H, uint16_t* __restrict__ y_bf16, float* __restrict__ out_f32) {
+  __shared__ int s_slot[32];
+  __shared__ float s_w[32];
+  __shared__ int s_n;
+  const int t = blockIdx.x;
+  if (threadIdx.x < 32) {
+    const int j = threadIdx.x;
+    int e = -1;
+    float wj = 0.0f;
+    if (j < k) {
+      e = ids[(size_t)t * k + j];
+      wj = w[(size_t)t * k + j];
+      if (e < 0 || e >= n_experts) e = -1;
+    }
+    const unsigned valid = __ballot_sync(0xFFFFFFFFu, e >= 0);
+    int rank = 0;
+    for (int o = 0; o < k; ++o) {
+      const int eo = __shfl_sync(0xFFFFFFFFu, e, o);
+      if (eo >= 0 && (eo < e || (eo == e && o < j))) ++rank;
+    }
+    if (e >= 0) {
+      s_slot[rank] = j;
+      s_w[rank] = wj;
+    }
+    if (j == 0) s_n = __popc(valid);
+  }
+  __syncthreads();
+  const int n = s_n;
+  const float* base = part + (size_t)t * k * H;
+  for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < n; ++i) {
+      const float4 v = *reinterpret_cast<const float4*>(base + (size_t)s_slot[i] * H + c);
+      const float wi = s_w[i];
+      acc.x += v.x * wi; acc.y += v.y * wi; acc.z += v.z * wi; acc.w += v.w * wi;
+    }
+    if (out_f32 != nullptr) *reinterpret_cast<float4*>(out_f32 + (size_t)t * H + c) = acc;
+    if (y_bf16 != nullptr) {
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(acc.x) | ((uint32_t)f32_to_bf16_bits(acc.y) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(acc.z) | ((uint32_t)f32_to_bf16_bits(acc.w) << 16);
+      *reinterpret_cast<uint2*>(y_bf16 + (size_t)t * H + c) = o;
+    }
   }
 }
 
@@ -377,17 +434,18 @@ void ep_launch_pack_meta_peer(const int32_t* topk_ids, const float* topk_w, int 
 
 void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts, int world, int cap,
                                 int slots, const unsigned long long* x_bases,
-                                const unsigned long long* out_bases, int H, int32_t* ids, float* w,
-                                unsigned long long* a_rows, unsigned long long* out_rows,
+                                const unsigned long long* out_bases, int H, int out_rows_per_token, int32_t* ids,
+                                float* w, unsigned long long* a_rows, unsigned long long* out_rows,
                                 cudaStream_t stream) {
+  expects(out_rows_per_token >= 1, "ep_unpack_meta_peer: out_rows_per_token must be positive");
   expects(cap > 0 && slots > 0 && world >= 1 && world <= 32 && H > 0 && H % 8 == 0,
           "ep_unpack_meta_peer: bad dimensions");
   expects(meta && recv_counts && x_bases && out_bases && ids && w && a_rows && out_rows,
           "ep_unpack_meta_peer: null buffer");
   const int n = world * cap;
   ep_unpack_meta_peer_kernel<<<(n + 255) / 256, 256, 0, stream>>>(meta, recv_counts, world, cap, slots,
-                                                                  x_bases, out_bases, H, ids, w, a_rows,
-                                                                  out_rows);
+                                                                  x_bases, out_bases, H, out_rows_per_token, ids,
+                                                                  w, a_rows, out_rows);
   VK_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -411,6 +469,15 @@ void ep_reset_status() {
   const int zero = 0;
   VK_CUDA_CHECK(cudaDeviceSynchronize());
   VK_CUDA_CHECK(cudaMemcpyToSymbol(g_ep_status, &zero, sizeof(int)));
+}
+
+void ep_launch_combine_slots(const float* part, const int32_t* ids, const float* w, int T, int k, int n_experts, int H,
+                             uint16_t* y_bf16, float* out_f32, cudaStream_t stream) {
+  expects(T >= 0 && k >= 1 && k <= 32 && H > 0 && H % 4 == 0 && n_experts > 0, "ep_combine_slots: bad dimensions");
+  if (T == 0) return;
+  expects(part && ids && w && (y_bf16 || out_f32), "ep_combine_slots: null buffer");
+  ep_combine_slots_kernel<<<T, 256, 0, stream>>>(part, ids, w, k, n_experts, H, y_bf16, out_f32);
+  VK_CUDA_CHECK(cudaGetLastError());
 }
 
 void ep_launch_combine(const float* rows, const int32_t* row_of, int T, int H, int world,

@@ -193,8 +193,8 @@ void fused_moe_mxfp4_rows(const uint16_t* const* a_rows, const uint8_t* w13, con
                           uint16_t* act_scratch, float* const* out_rows, int M, int hidden, int ispp,
                           int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                           float swiglu_limit, int activation, float beta, float linear_beta,
-                          const float* b13, const float* b2, int block_size, void* stream) {
-  const RowPtrs rows{a_rows, out_rows};
+                          const float* b13, const float* b2, int block_size, void* stream, bool store_slots) {
+  const RowPtrs rows{a_rows, out_rows, store_slots};
   run_fused(nullptr, w13, w13_scale, w2, w2_scale, topk_w, 0, act_scratch, nullptr, M, hidden, ispp,
             top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2,
             block_size, false, stream, &rows);

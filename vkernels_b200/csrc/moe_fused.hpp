@@ -80,13 +80,18 @@ size_t workspace_bytes_required_bf16(int max_EM, int hidden, int ispp, int n_loc
 struct RowPtrs {
   const uint16_t* const* a_rows;
   float* const* out_rows;
+  // false: every result row is added, times its routing weight, into out_rows[m] (system-scope
+  // reductions). true: out_rows[m] is the address of a [top_k, hidden] fp32 block and slot j's
+  // row (act @ w2^T + b2, unweighted) is STORED at its row j - plain 16-byte stores, no atomics;
+  // the owner of the block adds the slots in a fixed order afterwards (ep_combine_slots).
+  bool store_slots = false;
 };
 void fused_moe_mxfp4_rows(const uint16_t* const* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
                           const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
                           uint16_t* act_scratch, float* const* out_rows, int M, int hidden, int ispp,
                           int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                           float swiglu_limit, int activation, float beta, float linear_beta,
-                          const float* b13, const float* b2, int block_size, void* stream);
+                          const float* b13, const float* b2, int block_size, void* stream, bool store_slots = false);
 
 // The layer in four stages for tensor parallelism (reference moe_fused.hpp:265-286, same
 // argument lists plus the stream): w13 / w2 are this rank's K-shards ([E, 2*ispp, hidden_k/2] and

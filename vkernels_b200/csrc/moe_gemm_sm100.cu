@@ -83,9 +83,7 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 // dequant sets and two epilogue sets (the accumulator drains twice as fast, which is what its
 // MMA issuer waits for); a lone CTA (decode) runs three dequant sets and one epilogue set (its
 // epilogue is a few rounds, its bound is the expansion).
-// The fp8 form (see below) runs four dequant sets: its expansion is bound by the integer pipe, and
-// four warps per scheduler keep that pipe fed while the others wait on barriers.
-constexpr int dequant_sets(int ctas, bool mx = false) { return mx ? 4 : (ctas == 2 ? 2 : 3); }   // dequant warps per TMEM lane quarter
+constexpr int dequant_sets(int ctas, bool = false) { return ctas == 2 ? 2 : 3; }   // dequant warps per TMEM lane quarter
 constexpr int epi_sets(int ctas) { return ctas == 2 ? 2 : 1; }       // epilogue warps per lane quarter
 constexpr int block_threads(int ctas, bool mx) { return (4 + 4 * (dequant_sets(ctas, mx) + epi_sets(ctas))) * 32; }
 constexpr int kTmemCols = 512;
@@ -118,6 +116,8 @@ struct GemmParams {
   uint16_t* act;              // gate/up output [EM, n_feat]
   float* out;                 // down output [M, n_feat]
   float* const* out_rows;     // optional: address of each token's output row (may be another GPU's memory)
+  int store_rows;             // with out_rows: out_rows[m] is a [top_k, n_feat] block; slot j's row (act @ w2^T + b2,
+                              // unweighted) is STORED at row j instead of being added, weighted, into one row
   float* raw;                 // optional: plain fp32 result rows [EM, raw_ld] instead of the fused epilogue
   int raw_ld;                 //   (the tensor-parallel stage split: the caller reduces across ranks first)
   int k_base;                 // first column of the token rows this launch reduces over (K-sharded weights)
@@ -536,19 +536,22 @@ struct Ring {
 // p1, rows n..2n-1 are p2 - and ONE MMA per K block yields both partial products in adjacent
 // column ranges of the accumulator; the epilogue adds them and multiplies by s (unit token
 // scale factors inside the MMA).
-// MX = 0: bf16 forms; 32 or 64: the fp8 form for token tiles up to that many rows (with tiles up
-// to 32 rows two accumulators fit tensor memory and alternate between items, so an item's
-// epilogue overlaps the next item's MMAs).
+// MX = 0: bf16 forms; 32: the fp8 form, token tiles of up to 32 rows (an expert with more rows
+// becomes several items). Its tensor memory: a 64-column accumulator (two pieces x 32 tokens),
+// 4 columns of unit token scale factors, six A slots of 64 + 8 columns. Three dequant teams with
+// six slots means every team owns two slots and alternates between them: the slot a team needs
+// next was last used by its own stage before last, whose MMAs were issued a whole team period
+// ago - a team never waits for a slot.
 template <bool GATEUP, int KS, int CTAS, int MX = 0>
 __global__ void __launch_bounds__(block_threads(CTAS, MX != 0), 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
-  static_assert(MX == 0 || ((MX == 32 || MX == 64) && CTAS == 1 && KS == 256), "the fp8 form is a lone CTA with 256-K stages");
+  static_assert(MX == 0 || (MX == 32 && CTAS == 1 && KS == 256), "the fp8 form is a lone CTA with 256-K stages");
   constexpr int kThreads = block_threads(CTAS, MX != 0);
   // accumulator columns; the fp8 form keeps the two token pieces side by side
   constexpr int kAccCols = MX ? 2 * MX : acc_cols(KS, CTAS);
-  constexpr int kAccBufs = MX == 32 ? 2 : 1;
+  constexpr int kAccBufs = 1;
   constexpr int kSfbCol = kAccBufs * kAccCols;                        // fp8 form: 4 columns of unit token scale factors
   constexpr int kSlot0 = MX ? kSfbCol + 8 : kAccCols;                 // first A slot
   constexpr int kACols = MX ? KS / 4 + 8 : KS / 2;                    // columns of one A slot (fp8: 64 of values + 8 of scale factors)
@@ -745,6 +748,44 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           }
         }
       }
+    } else if (MX) {
+      // fp8 tokens, staged as [128-K half][piece 1 rows, piece 2 rows][128 bytes]. A stage is
+      // 4 to 8 small boxes (two pieces x two K halves x 16-row groups); one thread issuing them
+      // one after the other is slower than the stage's MMAs, so the lanes of the warp issue
+      // one box each. A half that sticks out past K is zero-filled by the copy and its bytes
+      // still count.
+      Ring b, lag;           // lag trails b by b_stages stages, on the A ring
+      int issued = 0;        // stages issued so far (all items)
+      bool ok = true;
+      for (int item = unit; item < n_items && ok; item += n_units) {
+        const TokTile tt = p.tiles[item / n_fgroups];
+        const int n_r16 = tt.n_rows >> 4;
+        for (int st = 0; st < n_stages; ++st, ++issued) {
+          if (issued >= p.b_stages) {
+            int w = 1;
+            if (lane == 0) w = mbar_wait(smem_u32(&bars->stage_done[lag.slot]), lag.phase, abort_flag, 3, 64) ? 1 : 0;
+            if (__shfl_sync(0xFFFFFFFFu, w, 0) == 0) {
+              ok = false;
+              break;
+            }
+            lag.advance(kAStages);
+          }
+          const uint32_t bar = smem_u32(&bars->b_full[b.slot]);
+          const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
+          const int k0 = st * KS;
+          const int n_half = min(2, (p.K - k0 + 127) / 128);
+          if (lane == 0) mbar_expect_tx(bar, tt.n_rows * 128 * n_half * 2);
+          __syncwarp();
+          const int per_piece = n_half * n_r16;
+          if (lane < 2 * per_piece) {
+            const int pc = lane / per_piece, rem = lane - pc * per_piece;
+            const int kh = rem / n_r16, rc = rem - kh * n_r16;
+            tma_load_2d(dst + kh * 2 * slice_bytes + (pc * tt.n_rows + rc * 16) * 128, &tmap_b, k0 + kh * 128,
+                        pc * p.piece_rows + tt.row0 + rc * 16, bar);
+          }
+          b.advance(p.b_stages);
+        }
+      }
     } else if (lane == 0) {
       Ring b, lag;           // lag trails b by b_stages stages, on the A ring
       int issued = 0;        // stages issued so far (all items)
@@ -762,23 +803,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t bar = smem_u32(&bars->b_full[b.slot]);
           const uint32_t dst = smem_u32(b_smem + b.slot * p.b_stage_bytes);
           const int k0 = st * KS;
-          if (MX) {
-            // fp8 tokens: [128-K half][piece 1 rows, piece 2 rows][128 bytes]; a half that sticks
-            // out past K is zero-filled by the copy, and its bytes still count
-            const int n_half = min(2, (p.K - k0 + 127) / 128);
-            mbar_expect_tx(bar, tt.n_rows * 128 * n_half * 2);
-            for (int pc = 0; pc < 2; ++pc) {
-              for (int kh = 0; kh < n_half; ++kh) {
-                const uint32_t d = dst + kh * 2 * slice_bytes + pc * tt.n_rows * 128;
-                const int row = pc * p.piece_rows + tt.row0;
-                int r = 0;
-                for (; r + 64 <= tt.n_rows; r += 64) tma_load_2d(d + r * 128, &tmap_b64, k0 + kh * 128, row + r, bar);
-                for (; r < tt.n_rows; r += 16) tma_load_2d(d + r * 128, &tmap_b, k0 + kh * 128, row + r, bar);
-              }
-            }
-            b.advance(p.b_stages);
-            continue;
-          }
           const int n_slices = min(kPieces, (p.K - k0) / 64);
           mbar_expect_tx(bar, tt.n_rows * 128 * n_slices);
           for (int sl = 0; sl < n_slices; ++sl) {
@@ -968,6 +992,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const int L = 32 * i + lane;
         sf_row[i] = GATEUP ? (((L >> 3) & 1) * 64 + (L >> 4) * 8 + (L & 7)) : L;
       }
+      static_assert(kAStages >= kTeams, "one A slot per team at least");
       int w_slot = team % p.w_stages, a_slot = team;
       uint32_t w_phase = (uint32_t)(team / p.w_stages) & 1u, a_phase = 0;
       int g_base = 0;                        // running index of the item's first stage
@@ -980,7 +1005,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint8_t* sf_src[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) sf_src[i] = sf_row[i] < rows_valid ? sc_tile + sf_row[i] * pitch : nullptr;
-        for (int kw = (team - g_base) & (kTeams - 1); kw < n_kw; kw += kTeams) {
+        for (int kw = (team + kTeams - g_base % kTeams) % kTeams; kw < n_kw; kw += kTeams) {
           if (!mbar_wait(smem_u32(&bars->w_full[w_slot]), w_phase, abort_flag, 8) ||
               !mbar_wait(smem_u32(&bars->stage_done[a_slot]), a_phase ^ 1u, abort_flag, 9)) {
             ok = false;
@@ -1163,6 +1188,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         } else {
           const int token = real ? flat / p.top_k : 0;
           float* orow = p.out_rows ? p.out_rows[token] : p.out + (size_t)token * p.n_feat;
+          if (p.store_rows && real) orow += (size_t)(flat - token * p.top_k) * p.n_feat;
           bars->tile_ref[j] = real ? reinterpret_cast<unsigned long long>(orow) : 0ull;
         }
         if (!GATEUP) bars->tile_w[j] = (real && p.topk_w != nullptr) ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
@@ -1327,7 +1353,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const float ts = bars->tile_s[t];
                     a.x *= ts; a.y *= ts; a.z *= ts; a.w *= ts;
                   }
-                  if (p.out_rows != nullptr)
+                  if (p.store_rows)   // plain 16-byte store of the slot's row; the home rank adds its slots in order
+                    *reinterpret_cast<float4*>(orow + h0) = make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w);
+                  else if (p.out_rows != nullptr)
                     red_add_v4_sys(orow + h0, (a.x + b4.x) * wgt, (a.y + b4.y) * wgt,
                                    (a.z + b4.z) * wgt, (a.w + b4.w) * wgt);
                   else
@@ -1778,7 +1806,7 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   // 16 KB): the deeper it is, the more weight bytes are in flight, which is what a decode-size
   // batch is bound by.
   constexpr int kAccCols = acc_cols(KS, CTAS);
-  constexpr int kAStages = MX ? (kTmemCols - 128 - 8) / (KS / 4 + 8) : (kTmemCols - kAccCols) / (KS / 2);
+  constexpr int kAStages = MX ? (kTmemCols - 2 * MX - 8) / (KS / 4 + 8) : (kTmemCols - kAccCols) / (KS / 2);
   constexpr int kThreads = block_threads(CTAS, MX != 0);
   const int max_smem = 227 * 1024;
   const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
@@ -1787,9 +1815,9 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
   p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
   // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot
-  // (the fp8 form keeps three token slots and gives the room to the packed-weight ring, whose
-  // depth is what covers the HBM latency)
-  int b_stages = CTAS == 2 ? kAStages : (MX ? 3 : (kAStages < 4 ? kAStages : 4)), scale_bufs = 2;
+  // (the fp8 form: token tiles are small - 8 KB a stage at 16 rows - but come a stage at a time
+  // from L2 with its full latency, so their ring is as deep as the A ring allows)
+  int b_stages = CTAS == 2 ? kAStages : (MX ? (p.max_tok <= 16 ? 6 : 4) : (kAStages < 4 ? kAStages : 4)), scale_bufs = 2;
   auto w_room = [&]() {
     return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
   };
@@ -1841,7 +1869,6 @@ template <bool GATEUP>
 void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                  bool use_pair, cudaStream_t stream, bool mx = false) {
   if (p.max_tok <= 32 && mx) launch_gemm_ks<GATEUP, 256, 1, 32>(tw, tb, tb64, p, stream);
-  else if (p.max_tok <= 64 && mx) launch_gemm_ks<GATEUP, 256, 1, 64>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
   else if (use_pair) launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
@@ -1977,6 +2004,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       float swiglu_limit, int activation, float beta, float linear_beta,
                       const float* b13, const float* b2, int block_size, cudaStream_t stream,
                       const RowPtrs* rows, uint16_t* y_bf16) {
+  const bool store_rows = rows != nullptr && rows->store_slots;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   const uint16_t* const* a_rows = rows ? rows->a_rows : nullptr;
   float* const* out_rows = rows ? rows->out_rows : nullptr;
@@ -1998,9 +2026,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // cover the rows of every expert id that fits an int32 row index.
   const uint64_t w13_rows_cap = (uint64_t)1 << 31;
   const TileChoice choice = choose_tiles(M, top_k, EM, block_size, hidden, ispp);
-  const int max_tok = choice.max_tok;
+  const bool mx = choice.max_tok <= 64 && small_fp8_mode();
+  const int max_tok = mx ? std::min(choice.max_tok, 32) : choice.max_tok;   // the fp8 form takes tiles of up to 32 rows
   const bool use_pair = choice.use_pair;
-  const bool mx = max_tok <= 64 && small_fp8_mode();
   // a small problem's tile list is built by an extra CTA of the row pre-pass (one launch less)
   const bool tiles_in_split = mx && EM / block_size <= 1024;
   if (!tiles_in_split)
@@ -2053,6 +2081,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   {  // down + combine
     GemmParams p = g;
     p.w_scale = w2_scale; p.bias = b2; p.topk_w = topk_w; p.out = out; p.out_rows = out_rows; p.tok_scale = scale_a;
+    p.store_rows = store_rows ? 1 : 0;
     p.K = ispp; p.n_feat = hidden; p.n_ftiles = (hidden + 127) / 128;
     if (ordered) {
       p.raw = partial;

@@ -10,6 +10,7 @@
 // rule used is the DeepSeek-V3 one: a group's score is the sum of its two
 // largest biased scores and only experts of the topk_group best groups stay
 // eligible.
+#include <algorithm>
 #include <atomic>
 #include "common.cuh"
 #include "moe_fused.hpp"
@@ -176,9 +177,10 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) total[n][j] = 0.0f;
 
-  // gridDim.z == 2 splits the reduction in two halves that are added into zeroed logits with
-  // atomics: a sum of two partials does not depend on their order, so the result stays
-  // reproducible, and a batch too small to fill the machine gets twice the CTAs.
+  // gridDim.z > 1 splits the reduction into slices so that a batch too small to fill the machine
+  // still does: two slices are added into zeroed logits with atomics (a sum of two partials does
+  // not depend on their order, so the result stays reproducible); more slices write one plane
+  // [T, E] each (`logits` then has gridDim.z planes) and a second kernel adds the planes in order.
   const int all_chunks = (H + MK - 1) / MK;
   const int ch_begin = (int)blockIdx.z * all_chunks / (int)gridDim.z;
   const int n_chunks = ((int)blockIdx.z + 1) * all_chunks / (int)gridDim.z;
@@ -228,15 +230,29 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
     for (int half = 0; half < 2; ++half) {
       const int t = r0 + half * 8;
       if (t >= T) continue;
-      if (gridDim.z == 1) {
-        if (e < E) logits[(size_t)t * E + e] = total[n][half * 2];
-        if (e + 1 < E) logits[(size_t)t * E + e + 1] = total[n][half * 2 + 1];
+      if (gridDim.z != 2) {
+        float* plane = logits + (size_t)blockIdx.z * T * E;
+        if (e < E) plane[(size_t)t * E + e] = total[n][half * 2];
+        if (e + 1 < E) plane[(size_t)t * E + e + 1] = total[n][half * 2 + 1];
       } else {
         if (e < E) atomicAdd(logits + (size_t)t * E + e, total[n][half * 2]);
         if (e + 1 < E) atomicAdd(logits + (size_t)t * E + e + 1, total[n][half * 2 + 1]);
       }
     }
   }
+}
+
+// logits[i] = planes[0][i] + planes[1][i] + ... in plane order (fixed: reproducible)
+__global__ void __launch_bounds__(256)
+sum_planes_kernel(const float* __restrict__ planes, int n_planes, size_t n, float* __restrict__ logits) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 acc = *reinterpret_cast<const float4*>(planes + i);
+  for (int z = 1; z < n_planes; ++z) {
+    const float4 v = *reinterpret_cast<const float4*>(planes + (size_t)z * n + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  *reinterpret_cast<float4*>(logits + i) = acc;
 }
 
 // Small batches: one warp per (token, expert) dot product, 128-bit loads, so a decode
@@ -385,12 +401,25 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
           x, wr, logits, T, H, E);
     } else {
       dim3 grid(t_tiles, (E + 63) / 64);
-      if ((int)(grid.x * grid.y) < sm_count() && H >= 4 * MK) {   // not enough CTAs for the machine: split K in two
-        grid.z = 2;
-        VK_CUDA_CHECK(cudaMemsetAsync(logits, 0, (size_t)T * E * sizeof(float), static_cast<cudaStream_t>(stream)));
+      const int ctas = (int)(grid.x * grid.y), chunks = (H + MK - 1) / MK;
+      cudaStream_t st = static_cast<cudaStream_t>(stream);
+      // not enough CTAs for the machine: split K - in up to eight slices of at least four chunks
+      int z = 1;
+      if (ctas < sm_count() && H >= 4 * MK) z = std::min(std::min(8, chunks / 4), (sm_count() + ctas - 1) / ctas);
+      const size_t n = (size_t)T * E;
+      if (z > 2 && n % 4 == 0) {
+        // one plane per slice in the stream's scratch (behind its first 4 KB), added in order afterwards
+        float* planes = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace_get(4096 + (size_t)z * n * sizeof(float), st)) + 4096);
+        grid.z = (unsigned)z;
+        router_logits_mma_kernel<64><<<grid, 256, sizeof(RouterSmem<64>), st>>>(x, wr, planes, T, H, E);
+        sum_planes_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(planes, z, n, logits);
+      } else {
+        if (z >= 2) {
+          grid.z = 2;
+          VK_CUDA_CHECK(cudaMemsetAsync(logits, 0, n * sizeof(float), st));
+        }
+        router_logits_mma_kernel<64><<<grid, 256, sizeof(RouterSmem<64>), st>>>(x, wr, logits, T, H, E);
       }
-      router_logits_mma_kernel<64><<<grid, 256, sizeof(RouterSmem<64>), static_cast<cudaStream_t>(stream)>>>(
-          x, wr, logits, T, H, E);
     }
   } else {
     dim3 grid((T + RT - 1) / RT, (E + RE - 1) / RE);

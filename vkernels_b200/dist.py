@@ -190,17 +190,24 @@ class CudaBackend:
                                                                limit_clocks, self._stream())
         nr.check(rc, "ep_flag_barrier")
 
-    def unpack_meta_peer(self, meta, recv_counts, world, cap, slots, x_bases, out_bases, H, ids, w, a_rows,
-                         out_rows):
+    def unpack_meta_peer(self, meta, recv_counts, world, cap, slots, x_bases, out_bases, H, out_rows_per_token, ids, w,
+                         a_rows, out_rows):
         with torch.cuda.device(self.device):
             rc = nr.load_library().vk_cuda_moe_ep_unpack_meta_peer(
                 meta.data_ptr(), recv_counts.data_ptr(), world, cap, slots, x_bases.data_ptr(),
-                out_bases.data_ptr(), H, ids.data_ptr(), w.data_ptr(), a_rows.data_ptr(),
+                out_bases.data_ptr(), H, out_rows_per_token, ids.data_ptr(), w.data_ptr(), a_rows.data_ptr(),
                 out_rows.data_ptr(), self._stream())
         nr.check(rc, "ep_unpack_meta_peer")
 
-    def experts_rows(self, a_rows, out_rows, ids, w):
-        self.layer.experts_rows(a_rows, out_rows, ids, w)
+    def experts_rows(self, a_rows, out_rows, ids, w, store_slots=False):
+        self.layer.experts_rows(a_rows, out_rows, ids, w, store_slots=store_slots)
+
+    def combine_slots(self, part, ids, w, n_experts, y):
+        T, k = ids.shape
+        with torch.cuda.device(self.device):
+            rc = nr.load_library().vk_cuda_moe_ep_combine_slots(part.data_ptr(), ids.data_ptr(), w.data_ptr(), T, k,
+                                                                n_experts, y.shape[1], y.data_ptr(), None, self._stream())
+        nr.check(rc, "ep_combine_slots")
 
     def combine(self, back_rows, row_of, T, H, world, out):
         with torch.cuda.device(self.device):
@@ -267,7 +274,8 @@ class ExpertParallelMoE:
             group = self.group if self.group is not None else dist.group.WORLD
             H = self.hidden
             x_sym = symm.empty((max_tokens, H), dtype=torch.bfloat16, device=self.device)
-            out_sym = symm.empty((max_tokens, H), dtype=torch.float32, device=self.device)
+            # one fp32 row per (token, slot): the owners of the experts store their results here
+            out_sym = symm.empty((max_tokens, self.slots, H), dtype=torch.float32, device=self.device)
             stride = 1 + 2 * self.slots
             meta_sym = symm.empty((self.world * max_tokens, stride), dtype=torch.int32, device=self.device)
             cnt_sym = symm.empty((32,), dtype=torch.int32, device=self.device)
@@ -315,7 +323,20 @@ class ExpertParallelMoE:
         self.backend.flag_barrier(peer["flag_bases"], self.world, self.rank, slot, peer["epoch"],
                                   self.BARRIER_LIMIT_CLOCKS)
 
+    def input_buffer(self, T: int) -> torch.Tensor:
+        """The first T rows of this rank's activation buffer in peer-visible memory ([T, H] bf16).
+        Activations written (or copied from the host) straight into it are read by the owners of
+        the experts where they lie: ``forward`` then skips its own copy."""
+        if self._peer is None:
+            raise RuntimeError("input_buffer needs the peer-memory form (enable_peer_memory)")
+        return self._peer["x"][:T]
+
     def _forward_peer(self, x: torch.Tensor, topk=None, logits=None) -> torch.Tensor:
+        """One step of the peer-memory form: route -> routing records to the owners (peer stores)
+        -> barrier -> local experts over all record slots, reading token rows where they live and
+        STORING every slot's result row into the home rank's [T, slots, H] buffer -> barrier ->
+        ordered sum of each token's slots on the home rank (bf16 out). No atomics and no
+        zeroing: every slot row is written exactly once per step."""
         T, H = x.shape
         world, rank, slots = self.world, self.rank, self.slots
         dev = x.device
@@ -330,41 +351,43 @@ class ExpertParallelMoE:
 
         mark("start")
         if topk is None:
-            ids, w = self.backend.route(x, logits=logits) if logits is not None else self.backend.route(x)
-            ids, w = ids[:, : self.top_k].contiguous(), w[:, : self.top_k].contiguous()
+            ids_full, w_full = self.backend.route(x, logits=logits) if logits is not None else self.backend.route(x)
         else:
-            ids, w = topk
+            ids_full, w_full = topk
+            if self.n_shared and ids_full.shape[1] == self.top_k:   # append the always-on slots
+                sh = torch.arange(self.num_experts, self.num_experts + self.n_shared, dtype=torch.int32, device=dev)
+                ids_full = torch.cat([ids_full, sh.expand(T, -1)], 1).contiguous()
+                w_full = torch.cat([w_full, torch.ones((T, self.n_shared), dtype=torch.float32, device=dev)], 1).contiguous()
+        ids, w = ids_full[:, : self.top_k].contiguous(), w_full[:, : self.top_k].contiguous()
         self._last_routing = (ids, w)
         mark("route")
-        # this rank's tokens and a zeroed output, where every rank can reach them
-        x_sym, out_sym = peer["x"][:T], peer["out"][:T]
-        x_sym.copy_(x)
-        out_sym.zero_()
+        # this rank's tokens where every rank can reach them (no copy when the caller wrote them there)
+        x_sym, part = peer["x"][:T], peer["out"][:T]
+        if x.data_ptr() != x_sym.data_ptr():
+            x_sym.copy_(x)
         # routing records straight into the destination ranks' receive areas, then the counts
         cap = peer["max_tokens"]
-        cursor = peer["cursor"]
-        cursor.zero_()
-        self.backend.pack_meta_peer(ids, w, self.n_shared, world, rank, self.begins, cursor, peer["meta_bases"],
+        self.backend.pack_meta_peer(ids, w, self.n_shared, world, rank, self.begins, peer["cursor"], peer["meta_bases"],
                                     peer["cnt_bases"], cap)
         mark("records")
-        # every rank's tokens, records and counts are in place and its output rows are zero
+        # every rank's tokens, records and counts are in place
         self._barrier(0)
         mark("barrier_in")
         r_ids, r_w, a_rows, out_rows = peer["ids"], peer["w"], peer["a_rows"], peer["out_rows"]
         self.backend.unpack_meta_peer(peer["meta"], peer["cnt"], world, cap, slots, peer["x_bases"],
-                                      peer["out_bases"], H, r_ids, r_w, a_rows, out_rows)
-        self.backend.experts_rows(a_rows, out_rows, r_ids, r_w)
+                                      peer["out_bases"], H, slots, r_ids, r_w, a_rows, out_rows)
+        self.backend.experts_rows(a_rows, out_rows, r_ids, r_w, store_slots=True)
         mark("experts")
         R_send = R_recv = local_slots = None
         if self.count_local_slots:   # host reads, for reporting only
-            R_send, R_recv = int(cursor.sum()), int(peer["cnt"][:world].sum())
+            R_recv = int(peer["cnt"][:world].sum())
             local_slots = int((r_ids >= 0).sum())
-        # every rank's additions into this rank's output rows are done
+        # every rank's stores into this rank's slot rows are done
         self._barrier(1)
         mark("barrier_out")
         out = torch.empty((T, H), dtype=x.dtype, device=dev)
-        out.copy_(out_sym)
-        mark("convert")
+        self.backend.combine_slots(part, ids_full, w_full, self.num_experts + self.n_shared, out)
+        mark("combine")
         phase_ms = None
         if self.time_phases:
             torch.cuda.synchronize(dev)
@@ -372,10 +395,10 @@ class ExpertParallelMoE:
         stride = 1 + 2 * slots
         known = R_recv is not None
         self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T, "form": "peer memory",
-                       "launches_per_step": 2 + 3 + 1 + (1 if world * cap * slots <= 1024 else 3) + 4,
-                       "dispatch_bytes": R_send * stride * 4 if known else None, "combine_bytes": 0,
+                       "launches_per_step": 2 + 2 + 1 + 1 + (1 if world * cap * slots <= 1024 else 3) + 4 + 1 + 1,
+                       "dispatch_bytes": R_recv * stride * 4 if known else None, "combine_bytes": 0,
                        "peer_read_bytes": R_recv * H * 2 if known else None,
-                       "peer_add_bytes": R_recv * H * 4 if known else None,
+                       "peer_store_bytes": local_slots * H * 4 if local_slots is not None else None,
                        "local_slots": local_slots, "phase_ms": phase_ms}
         return out
 

@@ -219,7 +219,7 @@ class FusedMoEMxfp4:
             y.copy_(out)
         return y
 
-    def experts_rows(self, a_rows, out_rows, topk_ids, topk_w):
+    def experts_rows(self, a_rows, out_rows, topk_ids, topk_w, store_slots: bool = False):
         """Alignment + the two grouped GEMMs on rows given by ADDRESS (int64 [R] each): reads
         every activation row where it lives and adds every result row where it belongs (see
         ``ops.fused_moe_mxfp4_rows_into``). The output rows must be zeroed by their owner."""
@@ -233,7 +233,8 @@ class FusedMoEMxfp4:
                                       self.w2_scale, topk_w.reshape(-1), sids, eids,
                                       top_k=topk_ids.shape[1], block_size=self.block_size,
                                       swiglu_limit=self.swiglu_limit, activation=self.activation,
-                                      beta=self.beta, linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+                                      beta=self.beta, linear_beta=self.linear_beta, b13=self.b13, b2=self.b2,
+                                      store_slots=store_slots)
 
     def forward(self, x: torch.Tensor, *, logits: torch.Tensor | None = None, out_bf16=None):
         """route -> align -> gate/up -> down+combine, all on the current stream."""
@@ -290,6 +291,57 @@ class FusedMoEMxfp4:
         out_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return out_host
+
+
+class HostPipeline:
+    """End-to-end serving loop over pinned host batches: the host-to-device copy of step i + 1,
+    the layer on step i and the device-to-host copy of step i - 1 run at the same time on three
+    streams (two device input buffers, two device output buffers; the layer itself runs one
+    step at a time on its stream). ``submit(x_host, y_host)`` enqueues a step and returns at once;
+    ``drain()`` waits for everything submitted. Every step still pays its own two copies - they
+    are merely off the critical path, as in a server that receives the next batch while it
+    computes the current one."""
+
+    def __init__(self, layer: "FusedMoEMxfp4", max_tokens: int | None = None, step=None):
+        self.layer = layer
+        dev = layer.device
+        T = max_tokens or layer.max_tokens
+        self.h2d, self.compute, self.d2h = (torch.cuda.Stream(device=dev) for _ in range(3))
+        self.x = [torch.empty((T, layer.hidden), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.y = [torch.empty((T, layer.hidden), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.x_free = [torch.cuda.Event() for _ in range(2)]     # the layer has consumed x[i]
+        self.y_free = [torch.cuda.Event() for _ in range(2)]     # y[i] has reached the host
+        self.n = 0
+        self._step = step or (lambda x, y: layer.forward(x, out_bf16=y))
+        with torch.cuda.device(dev), torch.cuda.stream(self.compute):
+            ops.reserve_workspace(layer._workspace_bytes(), dev)   # the compute stream's scratch block
+
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        i = self.n & 1
+        T = x_host.shape[0]
+        x, y = self.x[i][:T], self.y[i][:T]
+        with torch.cuda.stream(self.h2d):
+            if self.n >= 2:
+                self.h2d.wait_event(self.x_free[i])
+            x.copy_(x_host, non_blocking=True)
+            loaded = torch.cuda.Event()
+            loaded.record(self.h2d)
+        with torch.cuda.stream(self.compute):
+            self.compute.wait_event(loaded)
+            if self.n >= 2:
+                self.compute.wait_event(self.y_free[i])
+            self._step(x, y)
+            self.x_free[i].record(self.compute)
+            done = torch.cuda.Event()
+            done.record(self.compute)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(done)
+            y_host.copy_(y, non_blocking=True)
+            self.y_free[i].record(self.d2h)
+        self.n += 1
+
+    def drain(self) -> None:
+        self.d2h.synchronize()
 
 
 def layer_from_config(cfg, weights: dict, router: dict | None, *, max_tokens: int | None = None):

@@ -72,8 +72,12 @@ _SIGNATURES = {
     "vk_cuda_moe_down_preact": (c_int, [c_void_p] * 6 + [c_int] * 7 + [c_void_p]),
     "vk_cuda_moe_combine": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_void_p]),
     "vk_cuda_moe_ep_pack_meta_peer": (c_int, [c_void_p] * 2 + [c_int] * 5 + [c_void_p] * 4 + [c_int, c_void_p]),
-    "vk_cuda_moe_ep_unpack_meta_peer": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_void_p] * 2 + [c_int] +
+    "vk_cuda_moe_ep_unpack_meta_peer": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_void_p] * 2 + [c_int] * 2 +
                                         [c_void_p] * 5),
+    "vk_cuda_fused_moe_mxfp4_rows_store": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
+                                           [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p,
+                                            c_int, c_void_p]),
+    "vk_cuda_moe_ep_combine_slots": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p] * 3),
     "vk_cuda_moe_ep_flag_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p]),
     "vk_cuda_fused_moe_mxfp4_rows": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
                                      [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p,

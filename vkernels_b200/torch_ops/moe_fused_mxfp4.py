@@ -268,11 +268,13 @@ def fused_moe_mxfp4_bf16_into(y_bf16, act_scratch, hidden_states, w13, w13_scale
 def fused_moe_mxfp4_rows_into(act_scratch, a_rows, out_rows, w13, w13_scale, w2, w2_scale, topk_weights,
                               sorted_ids, expert_ids, *, top_k: int, block_size: int = 16,
                               swiglu_limit: float = 0.0, activation: int = SWIGLU, beta: float = 4.0,
-                              linear_beta: float = 25.0, b13=None, b2=None):
+                              linear_beta: float = 25.0, b13=None, b2=None, store_slots: bool = False):
     """The layer with row ADDRESSES in place of the activation and output tensors: ``a_rows`` /
     ``out_rows`` are int64 [M] device tensors holding, per token, the address of its bf16
     activation row and of its fp32 output row (which may be in another GPU's memory mapped into
-    this process). Results are added to the output rows; everything is caller-owned."""
+    this process). Results are added to the output rows; everything is caller-owned. With
+    ``store_slots`` an output address names a [top_k, hidden] fp32 block instead and slot j's
+    unweighted row is stored at its row j (no atomics; see ``vk_cuda_fused_moe_mxfp4_rows_store``)."""
     require(a_rows.dtype == torch.int64 and out_rows.dtype == torch.int64 and a_rows.dim() == 1 and
             a_rows.shape == out_rows.shape, "a_rows / out_rows must be int64 [M]")
     same_gpu_contiguous(a_rows, out_rows, w13, w13_scale, w2, w2_scale, topk_weights, sorted_ids, expert_ids,
@@ -286,7 +288,9 @@ def fused_moe_mxfp4_rows_into(act_scratch, a_rows, out_rows, w13, w13_scale, w2,
             "act_scratch must be bf16 [EM, ispp]")
     require(topk_weights.dtype == torch.float32 and topk_weights.numel() >= M * top_k, "topk_weights too small")
     with torch.cuda.device(a_rows.device):
-        rc = nr.load_library().vk_cuda_fused_moe_mxfp4_rows(
+        lib = nr.load_library()
+        fn = lib.vk_cuda_fused_moe_mxfp4_rows_store if store_slots else lib.vk_cuda_fused_moe_mxfp4_rows
+        rc = fn(
             _ptr(a_rows), _ptr(w13), _ptr(w13_scale), _ptr(w2), _ptr(w2_scale), _ptr(topk_weights),
             _ptr(act_scratch), _ptr(out_rows), M, hidden, ispp, top_k, _ptr(sorted_ids), _ptr(expert_ids), EM,
             float(swiglu_limit), int(activation), float(beta), float(linear_beta), _ptr(b13), _ptr(b2),
