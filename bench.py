@@ -484,7 +484,8 @@ def run_multi_gpu(args, cfg, T):
         A_in = layer.input_buffer(T_local)
         A_in.copy_(A)
         A = A_in
-    step = lambda: layer(A, logits=logits)
+    eager_step = lambda: layer(A, logits=logits)
+    step = eager_step
     barrier = lambda: dist.barrier()
 
     # Outside the timed region: every rank checks a seeded sample of ITS rows against the CPU
@@ -520,6 +521,13 @@ def run_multi_gpu(args, cfg, T):
         dist.destroy_process_group()
         sys.exit(3)
 
+    # The peer-memory step has no host reads and no collective calls, so it replays as one CUDA
+    # graph: at 8 ranks a step is ~20 kernels in a few hundred microseconds, which launched one by
+    # one from Python is bound by the host. VK_EP_GRAPH=0 times the eager step instead.
+    y_graph = None
+    if layer._peer is not None and os.environ.get("VK_EP_GRAPH", "1") == "1":
+        graph, y_graph = layer.capture(A, logits=logits)
+        step = graph.replay
     with ClockSampler(local) as clk:
         ms = time_steps(step, args.steps, args.warmup, barrier=barrier)
     t = torch.tensor([sum(ms)], device=dev)
@@ -530,10 +538,11 @@ def run_multi_gpu(args, cfg, T):
 
     # this rank's two GEMM kernels (every rank times its own; rank 0 reports its pair)
     layer.count_local_slots = True
-    g_ms, d_ms, _ = kernel_times(step, max(3, min(args.steps, 10)))
+    g_ms, d_ms, _ = kernel_times(eager_step, max(3, min(args.steps, 10)))
     layer.time_phases = True
-    step()
+    eager_step()
     stats = layer.last_stats()
+    stats["launch"] = "CUDA graph replay" if y_graph is not None else "eager"
     layer.count_local_slots = False
     layer.time_phases = False
     # load per rank: expert slots each rank computed in that step, slowest rank's phases
@@ -564,7 +573,11 @@ def run_multi_gpu(args, cfg, T):
 
     def e2e_step():
         xd.copy_(xh, non_blocking=True)
-        yh.copy_(layer(xd, logits=logits), non_blocking=True)
+        if y_graph is not None:     # xd is the buffer the captured step reads
+            step()
+            yh.copy_(y_graph, non_blocking=True)
+        else:
+            yh.copy_(layer(xd, logits=logits), non_blocking=True)
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):

@@ -333,9 +333,12 @@ int vk_cuda_moe_ep_combine_slots(const float* part, const int32_t* ids, const fl
  * writes) and waits until every entry [slot][*] of its own array has reached `epoch` (acquire).
  * Epochs must grow from call to call on a slot. The wait gives up after limit_clocks SM clocks
  * (at most 8e9): the kernel then records 200 + the missing rank in a status word that
- * vk_cuda_moe_kernel_status reports, and returns - a rank that left does not hang the others. */
+ * vk_cuda_moe_kernel_status reports, and returns - a rank that left does not hang the others.
+ * epoch_counter (device, [8] int32, zero at start, or NULL): when given, `epoch` is ignored and the
+ * kernel increments entry [slot] and uses its new value - the form a captured CUDA graph can
+ * replay; every rank must then run the barrier the same number of times. */
 int vk_cuda_moe_ep_flag_barrier(const uint64_t* flag_bases, int world, int rank, int slot, int epoch,
-                                long long limit_clocks, void* stream);
+                                long long limit_clocks, int32_t* epoch_counter, void* stream);
 int vk_cuda_fused_moe_mxfp4_rows(const uint64_t* a_rows, const uint8_t* w13, const uint8_t* w13_scale,
                                  const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
                                  uint16_t* act_scratch, const uint64_t* out_rows, int M, int hidden,

@@ -23,7 +23,7 @@ void sm100_reset_status();
 int ep_last_status();
 void ep_reset_status();
 void ep_launch_flag_barrier(const unsigned long long* flag_bases, int world, int rank, int slot, int epoch,
-                            long long limit_clocks, cudaStream_t stream);
+                            long long limit_clocks, int* epoch_counter, cudaStream_t stream);
 void launch_wait_timeout_probe(long long limit_clocks, cudaStream_t stream);
 void ep_launch_pack(const uint16_t* x, const int32_t* topk_ids, const float* topk_w, int T, int H,
                     int k, int n_shared, int world, int rank, const int32_t* expert_begin,
@@ -379,10 +379,10 @@ int vk_cuda_moe_ep_unpack_meta_peer(const int32_t* meta, const int32_t* recv_cou
 }
 
 int vk_cuda_moe_ep_flag_barrier(const uint64_t* flag_bases, int world, int rank, int slot, int epoch,
-                                long long limit_clocks, void* stream) {
+                                long long limit_clocks, int32_t* epoch_counter, void* stream) {
   VK_TRY
   vkc::ep_launch_flag_barrier(reinterpret_cast<const unsigned long long*>(flag_bases), world, rank, slot, epoch,
-                              limit_clocks, static_cast<cudaStream_t>(stream));
+                              limit_clocks, epoch_counter, static_cast<cudaStream_t>(stream));
   VK_CATCH(return VK_OK, VK_RETURN_CODE)
 }
 

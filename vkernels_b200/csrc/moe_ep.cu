@@ -311,10 +311,18 @@ ep_combine_slots_kernel(const float* __restrict__ part, const int32_t* __restric
 // return instead of spinning, and the host reads that status before trusting the step.
 __device__ int g_ep_status;
 
+// `epoch_counter` (optional): the epoch is taken from device memory instead of the argument -
+// entry [slot] is incremented by every call and its new value used - so a captured graph can
+// replay the barrier; every rank must then call the barrier the same number of times.
 __global__ void __launch_bounds__(32)
 ep_flag_barrier_kernel(const unsigned long long* __restrict__ flag_bases, int world, int rank, int slot,
-                       int epoch, long long limit_clocks) {
+                       int epoch, long long limit_clocks, int* __restrict__ epoch_counter) {
   const int d = threadIdx.x;
+  if (epoch_counter != nullptr) {
+    int e = 0;
+    if (d == 0) e = atomicAdd(epoch_counter + slot, 1) + 1;
+    epoch = __shfl_sync(0xFFFFFFFFu, e, 0);
+  }
   if (d >= world) return;
   __threadfence_system();
   int* theirs = reinterpret_cast<int*>(flag_bases[d]) + slot * world + rank;
@@ -450,11 +458,11 @@ void ep_launch_unpack_meta_peer(const int32_t* meta, const int32_t* recv_counts,
 }
 
 void ep_launch_flag_barrier(const unsigned long long* flag_bases, int world, int rank, int slot, int epoch,
-                            long long limit_clocks, cudaStream_t stream) {
+                            long long limit_clocks, int* epoch_counter, cudaStream_t stream) {
   expects(world >= 1 && world <= 32 && rank >= 0 && rank < world, "ep_flag_barrier: bad world/rank");
   expects(slot >= 0 && slot < 8 && flag_bases != nullptr, "ep_flag_barrier: bad slot or null flag table");
   expects(limit_clocks > 0 && limit_clocks <= 8000000000ll, "ep_flag_barrier: limit must be in (0, 8e9] clocks");
-  ep_flag_barrier_kernel<<<1, 32, 0, stream>>>(flag_bases, world, rank, slot, epoch, limit_clocks);
+  ep_flag_barrier_kernel<<<1, 32, 0, stream>>>(flag_bases, world, rank, slot, epoch, limit_clocks, epoch_counter);
   VK_CUDA_CHECK(cudaGetLastError());
 }
 

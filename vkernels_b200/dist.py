@@ -184,10 +184,10 @@ class CudaBackend:
                 self._stream())
         nr.check(rc, "ep_pack_meta_peer")
 
-    def flag_barrier(self, flag_bases, world, rank, slot, epoch, limit_clocks):
+    def flag_barrier(self, flag_bases, world, rank, slot, epoch_counter, limit_clocks):
         with torch.cuda.device(self.device):
-            rc = nr.load_library().vk_cuda_moe_ep_flag_barrier(flag_bases.data_ptr(), world, rank, slot, epoch,
-                                                               limit_clocks, self._stream())
+            rc = nr.load_library().vk_cuda_moe_ep_flag_barrier(flag_bases.data_ptr(), world, rank, slot, 0,
+                                                               limit_clocks, epoch_counter.data_ptr(), self._stream())
         nr.check(rc, "ep_flag_barrier")
 
     def unpack_meta_peer(self, meta, recv_counts, world, cap, slots, x_bases, out_bases, H, out_rows_per_token, ids, w,
@@ -290,7 +290,10 @@ class ExpertParallelMoE:
             n_rows = self.world * max_tokens
             peer = {"x": x_sym, "out": out_sym, "meta": meta_sym, "cnt": cnt_sym, "hx": hx, "ho": ho,
                     "x_bases": dev_ptrs(hx), "out_bases": dev_ptrs(ho), "meta_bases": dev_ptrs(hm),
-                    "cnt_bases": dev_ptrs(hc), "flags": flag_sym, "flag_bases": dev_ptrs(hf), "epoch": 0,
+                    "cnt_bases": dev_ptrs(hc), "flags": flag_sym, "flag_bases": dev_ptrs(hf),
+                    # barrier epochs live on the device (one counter per barrier slot), so a captured
+                    # step replays them; every rank runs the same number of barriers
+                    "epochs": torch.zeros(8, dtype=torch.int32, device=self.device),
                     "max_tokens": max_tokens,
                     # routing arrays and row addresses of the expert call, one per record slot
                     "ids": torch.empty((n_rows, self.slots), dtype=torch.int32, device=self.device),
@@ -318,10 +321,36 @@ class ExpertParallelMoE:
         """Flag barrier over the ranks of the peer-memory form, as a kernel on the current stream
         (bounded wait; see ``vk_cuda_moe_ep_flag_barrier``). Both slots advance once per step."""
         peer = self._peer
-        if slot == 0:
-            peer["epoch"] += 1
-        self.backend.flag_barrier(peer["flag_bases"], self.world, self.rank, slot, peer["epoch"],
+        self.backend.flag_barrier(peer["flag_bases"], self.world, self.rank, slot, peer["epochs"],
                                   self.BARRIER_LIMIT_CLOCKS)
+
+    def capture(self, x: torch.Tensor, logits=None):
+        """Captures one step of the peer-memory form on ``x`` (use ``input_buffer``) into a CUDA
+        graph; returns ``(graph, y)``. The step has no host reads and no collective calls - router,
+        record exchange, both flag barriers, the expert kernels and the combine are kernels on one
+        stream - so a replay costs one launch of host time instead of twenty, which is what a
+        sub-millisecond step at 8 ranks is otherwise bound by. Collective: every rank captures, and
+        afterwards every rank replays the same number of times."""
+        if self._peer is None:
+            raise RuntimeError("capture needs the peer-memory form (enable_peer_memory)")
+        from . import torch_ops as ops
+
+        self.time_phases = self.count_local_slots = False
+        layer = self.backend.layer
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            ops.reserve_workspace(layer._workspace_bytes(), self.device)   # this stream's scratch block
+            for _ in range(2):
+                self.forward(x, logits=logits)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y = self.forward(x, logits=logits)
+        self._capture_stream = side
+        return graph, y
 
     def input_buffer(self, T: int) -> torch.Tensor:
         """The first T rows of this rank's activation buffer in peer-visible memory ([T, H] bf16).

@@ -78,7 +78,7 @@ _SIGNATURES = {
                                            [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p,
                                             c_int, c_void_p]),
     "vk_cuda_moe_ep_combine_slots": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p] * 3),
-    "vk_cuda_moe_ep_flag_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p]),
+    "vk_cuda_moe_ep_flag_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p, c_void_p]),
     "vk_cuda_fused_moe_mxfp4_rows": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
                                      [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p,
                                       c_int, c_void_p]),
