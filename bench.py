@@ -313,9 +313,13 @@ def launches_per_step(T, slots):
     return 2 + (1 if T * slots <= 1024 else 3) + 4
 
 
-def decode_sweep(peaks, steps, warmup):
+def decode_sweep(peaks, steps, warmup, prepack=True, parity_tokens=8):
     """gpt-oss-20b-shaped layer, T in {1, 8, 32, 64, 128}: tokens/s and HBM roofline fraction on the
-    weight bytes of the experts the batch touches (+ activations, output, router weight)."""
+    weight bytes of the experts the batch touches (+ activations, output, router weight).
+    `prepack`: the layer objects keep the one-time prepacked form of their weights and run these
+    batches from it (a serving stack does this at model load); the checkpoint-layout time of
+    every batch size is printed beside it. The T = 8 result of the first weight copy is checked
+    against the CPU oracle."""
     from vkernels_b200.experts import layer_from_config
 
     cfg = syn.CONFIGS["c1"]
@@ -326,26 +330,49 @@ def decode_sweep(peaks, steps, warmup):
     r = syn.make_router(cfg, device=dev)
     for c in range(n_copies):
         w = syn.make_expert_weights(cfg, seed=cfg.seed + 17 * c, backend="torch", device=dev)
-        layers.append(layer_from_config(cfg, w, r, max_tokens=128))
+        layers.append(layer_from_config(cfg, w, r, max_tokens=128, prepack=prepack))
+        if c == 0:
+            w0 = w
+    prepacked = all(layer.prepacked is not None for layer in layers)
     out = []
     for T in cfg.T:
         A = syn.make_activations(cfg, T, backend="torch", device=dev)
-        ids, _ = layers[0].route(A)
+        ids, tw = layers[0].route(A)
         touched = int(torch.unique(ids).numel())
-        state = {"i": 0}
-        graphs = [layer.capture(A)[0] for layer in layers]   # one CUDA graph per weight copy
 
-        def step():
-            graphs[state["i"] % n_copies].replay()
-            state["i"] += 1
+        def timed():
+            state = {"i": 0}
+            graphs = [layer.capture(A)[0] for layer in layers]   # one CUDA graph per weight copy
 
-        ms = time_steps(step, max(steps, 20), max(warmup, 5))
-        med = statistics.median(ms)
+            def step():
+                graphs[state["i"] % n_copies].replay()
+                state["i"] += 1
+
+            ms = time_steps(step, max(steps, 20), max(warmup, 5))
+            return statistics.median(ms), min(ms)
+
+        med, lo = timed()
         bytes_alg = syn.decode_algorithmic_bytes(cfg, T, touched)
         gbs = bytes_alg / (med * 1e-3) / 1e9
-        out.append({"T": T, "experts_touched": touched, "launch": "CUDA graph replay", "ms_per_step": med, "ms_min": min(ms),
-                    "tokens_per_s": T / (med * 1e-3), "algorithmic_bytes": bytes_alg, "achieved_gbs": gbs,
-                    "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8tbs": gbs / 8000.0})
+        row = {"T": T, "experts_touched": touched, "launch": "CUDA graph replay", "ms_per_step": med, "ms_min": lo,
+               "weights": "prepacked at load" if prepacked else "checkpoint layout",
+               "tokens_per_s": T / (med * 1e-3), "algorithmic_bytes": bytes_alg, "achieved_gbs": gbs,
+               "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8tbs": gbs / 8000.0}
+        if prepacked:
+            if T == 8 and parity_tokens:
+                y = layers[0](A)
+                par = oracle_parity(cfg, A, y, ids, tw, w0, parity_tokens, cfg.seed, router=r)
+                row["parity"] = {k: par[k] for k in ("tokens", "max_abs", "rel_l2", "ok") if k in par}
+                if par["ok"] is False:
+                    print(json.dumps({"error": "decode parity check against the CPU oracle failed", "parity": par}), flush=True)
+                    sys.exit(3)
+            keep = [layer.prepacked for layer in layers]
+            for layer in layers:
+                layer.prepacked = None
+            row["checkpoint_layout_ms_per_step"], _ = timed()
+            for layer, pk in zip(layers, keep):
+                layer.prepacked = pk
+        out.append(row)
     return out
 
 
@@ -360,7 +387,7 @@ def run_single_gpu(args, cfg, T):
     r = syn.make_router(cfg, device=dev)
     A = syn.make_activations(cfg, T, backend="torch", device=dev)
     logits = syn.make_zipf_logits(cfg, T, device=dev) if cfg.zipf_alpha else None
-    layer = layer_from_config(cfg, w, r, max_tokens=T)
+    layer = layer_from_config(cfg, w, r, max_tokens=T, prepack=args.prepack)
     step = (lambda: layer(A, logits=logits))
 
     # outside the timed region: this very layer object against the CPU oracle on a token sample
@@ -618,6 +645,8 @@ def main():
     ap.add_argument("--parity-tokens", type=int, default=48, help="tokens per rank checked against the CPU oracle")
     ap.add_argument("--skip-parity", action="store_true",
                     help="profiling runs only: no oracle check and no end-to-end leg (single GPU)")
+    ap.add_argument("--prepack", action="store_true",
+                    help="single GPU, batches up to 256 tokens: run from weights prepacked at load (the decode sweep always does)")
     ap.add_argument("--weak", action="store_true", help="multi-GPU: keep the batch PER RANK fixed (weak scaling)")
     ap.add_argument("--no-decode-sweep", dest="decode_sweep", action="store_false")
     args = ap.parse_args()

@@ -149,6 +149,32 @@ int vk_cuda_fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const ui
                                  float linear_beta, const float* b13, const float* b2, int block_size, void* stream);
 size_t vk_cuda_moe_workspace_bytes_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N);
 
+/* Prepacked weights for decode-size batches (additive; the reference passes the checkpoint
+ * layout through untouched, src/python/vkernels/vllm_experts.py:531-582, and so do all entry
+ * points above). A one-time rewrite at model load: magnitude codes c >= 2 become c + 2, so that
+ * the tensor core's own e2m1 reading of a nibble is exactly twice the layer's table value
+ * (src/c/vkernels/kernels/moe_fused.cpp dequant table {0,.25,1,1.5,2,3}; the kernel halves the
+ * sums), groups with scale byte 0xFF become zero codes, and the scales are regrouped per
+ * (expert, 128-row work item, 256-K stage). The kernels then expand nothing.
+ *   which = 0: w13 [E, 2*ispp, hidden/2] + scales [E, 2*ispp, hidden/32]
+ *   which = 1: w2  [E, hidden, ispp/2]   + scales [E, hidden, ispp/32]
+ * vk_cuda_moe_prepack_sizes gives the two output sizes (the code buffer is the checkpoint size
+ * plus 128 rows and 64 bytes of padding); w_out must be 32-byte aligned. *nonfinite (device int)
+ * receives the number of 32-element groups holding code 6 or 7 (inf / NaN in this layer, not
+ * expressible in e2m1): a caller that reads a non-zero count must not use the prepacked form. */
+int vk_cuda_moe_prepack_sizes(int which, int E, int hidden, int ispp, size_t* w_bytes, size_t* sf_bytes);
+int vk_cuda_moe_prepack_weights(int which, const uint8_t* w, const uint8_t* scale, int E, int hidden, int ispp,
+                                uint8_t* w_out, uint8_t* sf_out, int* nonfinite, void* stream);
+/* vk_cuda_fused_moe_mxfp4_bf16 on prepacked weights (codes + regrouped scales of both sets).
+ * Serves batches whose token tiles stay within 64 rows (M <= 256 always does); larger batches
+ * return VK_ERROR_INVALID_ARGUMENT and belong to the checkpoint-layout entry points. */
+int vk_cuda_fused_moe_mxfp4_bf16_prepacked(const uint16_t* A, const uint8_t* w13_codes, const uint8_t* w13_sf,
+                                           const uint8_t* w2_codes, const uint8_t* w2_sf, const float* topk_w,
+                                           uint16_t* act_scratch, uint16_t* y, int M, int hidden, int ispp, int top_k,
+                                           const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                                           float swiglu_limit, int activation, float beta, float linear_beta,
+                                           const float* b13, const float* b2, int block_size, void* stream);
+
 /* Router. The reference has no router in this path; semantics follow its GPU
  * routing ops (src/python/vkernels/torch_ops/tokenspeed_amd/routing.py:58-145,
  * torch_ops/glm_router.py:43-88,184-262).

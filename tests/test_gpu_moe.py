@@ -302,6 +302,113 @@ def test_bf16_form_with_ordered_combine(name, T):
     assert_close_bf16(got if tokens is None else got[tokens], ref, f"bf16 form {name} T={T}", got_is_bf16=True)
 
 
+def _ocp_decode(codes_u8, K):
+    """Prepacked code bytes [rows, K/2] -> values as the tensor core reads e2m1, halved."""
+    ocp = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)
+    lo, hi = codes_u8 & 15, codes_u8 >> 4
+    nib = np.stack([lo, hi], axis=-1).reshape(codes_u8.shape[0], K)
+    return np.where(nib & 8, -1.0, 1.0).astype(np.float32) * ocp[nib & 7] * 0.5
+
+
+def test_prepack_rewrites_codes_and_scales_exactly():
+    """The prepacked codes, read with the e2m1 table and halved, are the layer's table values;
+    0xFF groups become zeros with scale 1; the regrouped scales sit where the kernel reads
+    them; inf / NaN codes are counted."""
+    cfg = syn.scaled(syn.CONFIGS["c1"], H=320, I=192, E=3)      # K = 320: one and a quarter stages; down tiles 128 + 128 + 64 rows
+    w = syn.make_expert_weights(cfg, device=DEV)
+    w13s = w["w13_scale"].clone()
+    w13s[1, 5, 3] = 0xFF
+    w13s[2, 100, 0] = 0xFF
+    pk = ops.prepack_weights(w["w13"], w13s, w["w2"], w["w2_scale"])
+    assert pk.usable and pk.nonfinite == 0
+    table = np.array([0, .25, 1, 1.5, 2, 3], np.float32)
+    for which, (wt, sc, codes, sf, K, n_feat) in enumerate([
+            (w["w13"], w13s, pk.w13_codes, pk.w13_sf, cfg.H, cfg.I), (w["w2"], w["w2_scale"], pk.w2_codes, pk.w2_sf, cfg.I, cfg.H)]):
+        raw = to_np(wt).reshape(-1, K // 2)
+        scn = to_np(sc).reshape(-1, K // 32)
+        rows = raw.shape[0]
+        got = _ocp_decode(to_np(codes)[: rows * (K // 2)].reshape(rows, K // 2), K)
+        nib = np.stack([raw & 15, raw >> 4], axis=-1).reshape(rows, K)
+        want = np.where(nib & 8, -1.0, 1.0).astype(np.float32) * table[nib & 7]
+        want = want * (np.repeat(scn, 32, axis=1) != 0xFF)
+        assert np.array_equal(got, want), which
+        assert not to_np(codes)[rows * (K // 2):].any(), "padding must be zero"
+        # scales: [E][tile][stage][128 accumulator rows][8 groups]
+        n_ft = n_feat // 64 if which == 0 else (n_feat + 127) // 128
+        n_kw = (K + 255) // 256
+        sft = to_np(sf).reshape(cfg.E, n_ft, n_kw, 128, 8)
+        rows_e = rows // cfg.E
+        for e, f, L in [(0, 0, 0), (1, 0, 13), (2, n_ft - 1, 127), (1, 1, 72), (2, 1, 36)]:
+            if which == 0:
+                sr = ((L >> 3) & 1) * 64 + (L >> 4) * 8 + (L & 7)
+                row = f * 64 + sr if sr < 64 else n_feat + f * 64 + sr - 64
+            else:
+                row = f * 128 + L if f * 128 + L < n_feat else -1
+            for kw in range(n_kw):
+                for b in range(8):
+                    kb = kw * 8 + b
+                    want_b = 0x7F
+                    if row >= 0 and kb < K // 32:
+                        want_b = int(scn[e * rows_e + row, kb])
+                        want_b = 0x7F if want_b == 0xFF else want_b
+                    assert int(sft[e, f, kw, L, b]) == want_b, (which, e, f, L, kw, b)
+    bad = syn.make_expert_weights(cfg, codes="all", device=DEV)
+    assert not ops.prepack_weights(bad["w13"], bad["w13_scale"], bad["w2"], bad["w2_scale"]).usable
+
+
+@pytest.mark.parametrize("name,T", [("c0", 64), ("c1", 1), ("c1", 8), ("c1", 64), ("c1", 128), ("c4", 16), ("c4", 256)])
+def test_prepacked_decode_form(name, T):
+    """vk_cuda_fused_moe_mxfp4_bf16_prepacked: within the layer's tolerance of the oracle, within
+    bf16 rounding of the checkpoint-layout form, bit-identical from run to run, with biases and
+    with a 0xFF (zero) scale group in the weights."""
+    cfg = syn.CONFIGS[name]
+    w, A, r = make_case(cfg, T, backend="torch")
+    w["w13_scale"][0, 3, 1] = 0xFF
+    w["w2_scale"][1 % w["w2"].shape[0], 7, 0] = 0xFF
+    logits = syn.make_zipf_logits(cfg, T, device=DEV) if cfg.zipf_alpha else None
+    ids_np, tw_np, _ = oracle_route(cfg, A, r, logits=None if logits is None else to_np(logits))
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    E = w["w13"].shape[0]
+    rng = np.random.default_rng(T + 5)
+    b13 = torch.from_numpy(rng.standard_normal((E, 2 * cfg.I)).astype(np.float32) * 0.1).to(DEV)
+    b2 = torch.from_numpy(rng.standard_normal((E, cfg.H)).astype(np.float32) * 0.1).to(DEV)
+    pk = ops.prepack_weights(w["w13"], w["w13_scale"], w["w2"], w["w2_scale"])
+    assert pk.usable
+    sids, eids, _ = ops.moe_align_block_size(ids, E, 16)
+    act = torch.zeros((sids.numel(), cfg.I), dtype=torch.bfloat16, device=DEV)
+    kw = dict(top_k=ids.shape[1], swiglu_limit=cfg.swiglu_limit, b13=b13, b2=b2)
+    ys = []
+    for _ in range(2):
+        y = torch.full((T, cfg.H), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.fused_moe_mxfp4_bf16_prepacked_into(y, act, A, pk, tw.reshape(-1).contiguous(), sids, eids, **kw)
+        torch.cuda.synchronize()
+        ops.kernel_status()
+        ys.append(y.clone())
+    assert torch.equal(ys[0], ys[1]), "the prepacked form must be bit-reproducible"
+    base = torch.empty((T, cfg.H), dtype=torch.bfloat16, device=DEV)
+    ops.fused_moe_mxfp4_bf16_into(base, act, A, w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], tw.reshape(-1).contiguous(),
+                                  sids, eids, **kw)
+    assert_close_bf16(to_np(ys[0].float()), to_np(base.float()), f"prepacked vs checkpoint layout {name} T={T}", got_is_bf16=True)
+    tokens = None if T <= 64 else np.sort(rng.choice(T, 48, replace=False))
+    ref = oracle_layer(A, w, ids, tw, tokens=tokens, swiglu_limit=cfg.swiglu_limit, b13=to_np(b13), b2=to_np(b2))
+    got = to_np(ys[0].float())
+    assert_close_bf16(got if tokens is None else got[tokens], ref, f"prepacked form {name} T={T}", got_is_bf16=True)
+
+
+def test_prepacked_form_refuses_prefill_batches():
+    cfg = syn.scaled(syn.CONFIGS["c1"], H=256, I=128, E=2, top_k=1)
+    T = 2048                                       # 1024 rows per expert: far beyond a 64-row tile
+    w, A, r = make_case(cfg, T, backend="torch")
+    ids_np, tw_np, _ = oracle_route(cfg, A, r)
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    pk = ops.prepack_weights(w["w13"], w["w13_scale"], w["w2"], w["w2_scale"])
+    sids, eids, _ = ops.moe_align_block_size(ids, cfg.E, 16)
+    act = torch.zeros((sids.numel(), cfg.I), dtype=torch.bfloat16, device=DEV)
+    y = torch.zeros((T, cfg.H), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="decode-size"):
+        ops.fused_moe_mxfp4_bf16_prepacked_into(y, act, A, pk, tw.reshape(-1).contiguous(), sids, eids, top_k=1)
+
+
 def test_host_pointer_abi():
     """vk_fused_moe_mxfp4 with HOST buffers (the CPU entry point's signature): copies in,
     kernels, copies out; accumulates into `out` like the reference."""

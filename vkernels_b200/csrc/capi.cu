@@ -175,6 +175,30 @@ size_t vk_cuda_moe_workspace_bytes_bf16(int max_EM, int hidden, int ispp, int n_
   return vkc::workspace_bytes_required_bf16(max_EM, hidden, ispp, n_local_experts, N);
 }
 
+int vk_cuda_moe_prepack_sizes(int which, int E, int hidden, int ispp, size_t* w_bytes, size_t* sf_bytes) {
+  VK_TRY
+  vkc::prepack_sizes(which, E, hidden, ispp, w_bytes, sf_bytes);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+int vk_cuda_moe_prepack_weights(int which, const uint8_t* w, const uint8_t* scale, int E, int hidden, int ispp,
+                                uint8_t* w_out, uint8_t* sf_out, int* nonfinite, void* stream) {
+  VK_TRY
+  vkc::prepack_weights(which, w, scale, E, hidden, ispp, w_out, sf_out, nonfinite, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+int vk_cuda_fused_moe_mxfp4_bf16_prepacked(const uint16_t* A, const uint8_t* w13_codes, const uint8_t* w13_sf,
+                                           const uint8_t* w2_codes, const uint8_t* w2_sf, const float* topk_w,
+                                           uint16_t* act_scratch, uint16_t* y, int M, int hidden, int ispp, int top_k,
+                                           const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
+                                           float swiglu_limit, int activation, float beta, float linear_beta,
+                                           const float* b13, const float* b2, int block_size, void* stream) {
+  VK_TRY
+  vkc::fused_moe_mxfp4_bf16_prepacked(A, w13_codes, w13_sf, w2_codes, w2_sf, topk_w, act_scratch, y, M, hidden, ispp,
+                                      top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation, beta, linear_beta,
+                                      b13, b2, block_size, stream);
+  VK_CATCH(return VK_OK, VK_RETURN_CODE)
+}
+
 int vk_cuda_moe_router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H,
                               int E, void* stream) {
   VK_TRY

@@ -24,7 +24,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                       float swiglu_limit, int activation, float beta, float linear_beta,
                       const float* b13, const float* b2, int block_size, cudaStream_t stream,
-                      const RowPtrs* rows, uint16_t* y_bf16);
+                      const RowPtrs* rows, uint16_t* y_bf16, bool w4);
 size_t sm100_workspace_bytes(int EM, int hidden, int ispp);
 size_t sm100_workspace_bytes_ordered(int EM, int hidden, int ispp, int N);
 
@@ -152,7 +152,7 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
                float* out, int M, int hidden, int ispp, int top_k, const int32_t* sorted_ids,
                const int32_t* expert_ids, int EM, float swiglu_limit, int activation, float beta,
                float linear_beta, const float* b13, const float* b2, int block_size, bool kmajor,
-               void* stream, const RowPtrs* rows = nullptr, uint16_t* y_bf16 = nullptr) {
+               void* stream, const RowPtrs* rows = nullptr, uint16_t* y_bf16 = nullptr, bool w4 = false) {
   expects(!kmajor, "fused_moe_mxfp4: the K-major weight layout is not supported");
   expects(M >= 0 && EM >= 0 && top_k > 0, "fused_moe_mxfp4: bad M / EM / top_k");
   expects(hidden > 0 && hidden % 64 == 0, "fused_moe_mxfp4: hidden must be a multiple of 64");
@@ -176,6 +176,7 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
     expects(top_k <= 32 && hidden % 4 == 0, "fused_moe_mxfp4_bf16: at most 32 slots per token");
     expects((reinterpret_cast<uintptr_t>(y_bf16) & 7u) == 0, "fused_moe_mxfp4_bf16: y must be 8-byte aligned");
   }
+  expects(!w4 || get_moe_impl() == MoeImpl::kTcgen05, "fused_moe_mxfp4_bf16_prepacked: only the tcgen05 path reads prepacked weights");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (get_moe_impl() == MoeImpl::kSimt)
     launch_moe_simt(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M, hidden,
@@ -184,7 +185,7 @@ void run_fused(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, 
   else
     launch_moe_sm100(A, w13, w13_scale, w2, w2_scale, topk_w, w_sorted, act_scratch, out, M,
                      hidden, ispp, top_k, sorted_ids, expert_ids, EM, swiglu_limit, activation,
-                     beta, linear_beta, b13, b2, block_size, s, rows, y_bf16);
+                     beta, linear_beta, b13, b2, block_size, s, rows, y_bf16, w4);
 }
 }  // namespace
 
@@ -221,6 +222,18 @@ void fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const uint8_t* 
   run_fused(A, w13, w13_scale, w2, w2_scale, topk_w, 0, act_scratch, nullptr, M, hidden, ispp, top_k, sorted_ids,
             expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2, block_size, false, stream, nullptr,
             y_bf16);
+}
+
+void fused_moe_mxfp4_bf16_prepacked(const uint16_t* A, const uint8_t* w13_codes, const uint8_t* w13_sf,
+                                    const uint8_t* w2_codes, const uint8_t* w2_sf, const float* topk_w,
+                                    uint16_t* act_scratch, uint16_t* y_bf16, int M, int hidden, int ispp, int top_k,
+                                    const int32_t* sorted_ids, const int32_t* expert_ids, int EM, float swiglu_limit,
+                                    int activation, float beta, float linear_beta, const float* b13, const float* b2,
+                                    int block_size, void* stream) {
+  expects(y_bf16 != nullptr || M == 0, "fused_moe_mxfp4_bf16_prepacked: y must not be null");
+  run_fused(A, w13_codes, w13_sf, w2_codes, w2_sf, topk_w, 0, act_scratch, nullptr, M, hidden, ispp, top_k, sorted_ids,
+            expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2, block_size, false, stream, nullptr,
+            y_bf16, true);
 }
 
 size_t workspace_bytes_required_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N) {

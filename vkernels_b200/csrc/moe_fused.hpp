@@ -73,6 +73,32 @@ void fused_moe_mxfp4_bf16(const uint16_t* A, const uint8_t* w13, const uint8_t* 
                           float linear_beta, const float* b13, const float* b2, int block_size, void* stream);
 size_t workspace_bytes_required_bf16(int max_EM, int hidden, int ispp, int n_local_experts, int N);
 
+// Prepacked weights for decode-size batches. The checkpoint layout costs a decode step integer
+// work per weight (nibble -> operand byte) that bounds it below the memory rate; a one-time
+// rewrite at model load removes it: every magnitude code c >= 2 becomes c + 2, which makes the
+// tensor core's own e2m1 reading of the nibble exactly twice this layer's table value
+// ({0, .25, 1, 1.5, 2, 3} -> {0, .5, 2, 3, 4, 6}; the epilogue halves the sums), groups with
+// scale byte 0xFF (zero in this layer) become zero codes with scale 1, and the scales are
+// regrouped per (expert, 128-row work item, 256-K stage). Same size as the checkpoint form
+// (+ 128 rows of padding). The layer's codes 6 and 7 (inf / NaN) cannot be expressed: `nonfinite`
+// (device int) receives the number of 32-element groups holding one, and a caller that reads a
+// non-zero count must keep that weight set on the checkpoint-layout entry points.
+//   which = 0: w13 [E, 2*ispp, hidden/2] + scales [E, 2*ispp, hidden/32]
+//   which = 1: w2  [E, hidden, ispp/2]   + scales [E, hidden, ispp/32]
+// w_out must be 32-byte aligned; sizes from prepack_sizes.
+void prepack_sizes(int which, int E, int hidden, int ispp, size_t* w_bytes, size_t* sf_bytes);
+void prepack_weights(int which, const uint8_t* w, const uint8_t* scale, int E, int hidden, int ispp, uint8_t* w_out,
+                     uint8_t* sf_out, int* nonfinite, void* stream);
+// fused_moe_mxfp4_bf16 on prepacked weights. Serves batches whose token tiles stay within 64 rows
+// (M <= 256 always does); larger batches are refused - they belong to the checkpoint-layout
+// entry points, whose prefill forms amortise the expansion over hundreds of tokens.
+void fused_moe_mxfp4_bf16_prepacked(const uint16_t* A, const uint8_t* w13_codes, const uint8_t* w13_sf,
+                                    const uint8_t* w2_codes, const uint8_t* w2_sf, const float* topk_w,
+                                    uint16_t* act_scratch, uint16_t* y_bf16, int M, int hidden, int ispp, int top_k,
+                                    const int32_t* sorted_ids, const int32_t* expert_ids, int EM, float swiglu_limit,
+                                    int activation, float beta, float linear_beta, const float* b13, const float* b2,
+                                    int block_size, void* stream);
+
 // Row addresses instead of base pointers: token m's activation row is read at a_rows[m] and
 // its result is added at out_rows[m] (hidden bf16 / fp32 values each, 16-byte aligned). The rows
 // may live in another GPU's memory mapped into this process (peer loads and reductions over

@@ -83,13 +83,22 @@ constexpr int kWStageBytes = kRows * 128;          // 16 KB
 // dequant sets and two epilogue sets (the accumulator drains twice as fast, which is what its
 // MMA issuer waits for); a lone CTA (decode) runs three dequant sets and one epilogue set (its
 // epilogue is a few rounds, its bound is the expansion).
-constexpr int dequant_sets(int ctas, bool = false) { return ctas == 2 ? 2 : 3; }   // dequant warps per TMEM lane quarter
+// (the prepacked-fp4 form expands nothing: one set of four warps only copies scale factors)
+constexpr int dequant_sets(int ctas, bool = false, bool w4 = false) { return w4 ? 1 : (ctas == 2 ? 2 : 3); }   // dequant warps per TMEM lane quarter
 constexpr int epi_sets(int ctas) { return ctas == 2 ? 2 : 1; }       // epilogue warps per lane quarter
-constexpr int block_threads(int ctas, bool mx) { return (4 + 4 * (dequant_sets(ctas, mx) + epi_sets(ctas))) * 32; }
+constexpr int block_threads(int ctas, bool mx, bool w4 = false) { return (4 + 4 * (dequant_sets(ctas, mx, w4) + epi_sets(ctas))) * 32; }
+// Prepacked-fp4 form: a weight stage in shared memory is 128 rows x 256 K as the copy engine
+// unpacks them (16 nibbles in the low 8 bytes of every 16: 256 bytes a row, 128-K halves one
+// after the other); the stage's scale factors [128 rows][8 groups] are read from global memory.
+constexpr int kW4TileBytes = kRows * 128;                  // one 128-K half of a stage: 16 KB
+constexpr int kW4SfBytes = kRows * 8;                      // 1 KB
+constexpr int kW4StageBytes = 2 * kW4TileBytes;            // 32 KB
 constexpr int kTmemCols = 512;
 constexpr int kEpiPitch = 72;                     // bf16 per staged token row: 64 features + 16 bytes against bank conflicts
 constexpr int kEpiStageBytes = 2 * 2 * 32 * kEpiPitch * 2;   // gate/up epilogue staging (two rounds per set, up to two sets)
 constexpr int kEpiStageDownBytes = 4 * 32 * 32 * 4;   // down epilogue: one 32 x 32 fp32 block per warp
+// what a launch really stages: a lone CTA runs one epilogue set, half of the above
+constexpr int epi_stage_bytes(bool gateup, int ctas) { return (gateup ? kEpiStageBytes : kEpiStageDownBytes) / (ctas == 2 ? 1 : 2); }
 // Lone-CTA form: byte -> bf16 pair lookup table in shared memory, one copy per bank (lane l reads
 // word 32 * byte + l), so a warp's 32 lookups of different bytes are one conflict-free access.
 constexpr int kLutBytes = 256 * 32 * 4;
@@ -227,6 +236,26 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
+// Prefetch of a contiguous range into L2 (no shared-memory destination, no barrier).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
                                              uint32_t bar) {
   asm volatile(
@@ -299,6 +328,18 @@ __device__ __forceinline__ void tc_mma_mx(uint32_t d_tmem, uint32_t a_tmem, uint
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], [%1], %2, %3, [%5], [%6], p;\n"
       "}\n" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// The same with A read from shared memory through a descriptor (e2m1 weights as the copy engine unpacked them).
+__device__ __forceinline__ void tc_mma_mx_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() {
@@ -471,8 +512,9 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
 // Block-scaled instruction descriptor: A e5m2 (format 1, bits 7-9), B e4m3 (format 0), both
 // K-major, N >> 3 at bit 17, ue8m0 scale factors (bit 23), M >> 4 at bit 24; the byte of the
 // scale-factor column that holds this K block goes to bits 29-30 (A) and 4-5 (B) per instruction.
-__device__ __forceinline__ uint32_t make_idesc_mx(int n) {
-  return (1u << 7) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+// (a_format 5 = e2m1, the prepacked-fp4 form)
+__device__ __forceinline__ uint32_t make_idesc_mx(int n, uint32_t a_format = 1u) {
+  return (a_format << 7) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
 }
 __device__ __forceinline__ uint32_t make_idesc(int n, int m = 128) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -542,20 +584,37 @@ struct Ring {
 // six slots means every team owns two slots and alternates between them: the slot a team needs
 // next was last used by its own stage before last, whose MMAs were issued a whole team period
 // ago - a team never waits for a slot.
-template <bool GATEUP, int KS, int CTAS, int MX = 0>
-__global__ void __launch_bounds__(block_threads(CTAS, MX != 0), 1)
+//
+// W4 (with MX = 32): the prepacked-fp4 form. The weights were rewritten once, when the layer was
+// built, into codes whose e2m1 reading by the tensor core is twice the layer's table value
+// (0, .25, 1, 1.5, 2, 3 -> 0, .5, 2, 3, 4, 6; the epilogue halves the sums), so nothing is
+// expanded at all: the copy engine unpacks the nibbles into the padded shared-memory form the
+// MMA reads A from (one 5-D box per stage puts the rows into accumulator order), and the dequant
+// warps shrink to one set that copies each stage's scale factors (prepacked as [stage][128
+// rows][8]) from global memory into tensor memory. What a small-N MMA costs is its issuing
+// thread (about a hundred cycles an instruction), so two warps issue, every other stage each,
+// into two accumulators that the epilogue adds.
+template <bool GATEUP, int KS, int CTAS, int MX = 0, bool W4 = false>
+__global__ void __launch_bounds__(block_threads(CTAS, MX != 0, W4), 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_b64, const GemmParams p) {
   static_assert(MX == 0 || (MX == 32 && CTAS == 1 && KS == 256), "the fp8 form is a lone CTA with 256-K stages");
-  constexpr int kThreads = block_threads(CTAS, MX != 0);
+  static_assert(!W4 || MX == 32, "the prepacked-fp4 form is a variant of the fp8 form");
+  constexpr int kThreads = block_threads(CTAS, MX != 0, W4);
+  constexpr int kWBytes = W4 ? kW4StageBytes : kWStageBytes;         // one slot of the weight ring
   // accumulator columns; the fp8 form keeps the two token pieces side by side
   constexpr int kAccCols = MX ? 2 * MX : acc_cols(KS, CTAS);
   constexpr int kAccBufs = 1;
-  constexpr int kSfbCol = kAccBufs * kAccCols;                        // fp8 form: 4 columns of unit token scale factors
+  // Prepacked-fp4 form: the issuing thread, not the tensor core, is what a small-N MMA costs
+  // (about a hundred cycles an instruction whatever N is), so TWO warps issue, each every
+  // other stage into its own accumulator; the epilogue adds the two.
+  constexpr int kIssuers = W4 ? 2 : 1;
+  constexpr int kSfbCol = kAccBufs * kAccCols * kIssuers;             // fp8 form: 4 columns of unit token scale factors
   constexpr int kSlot0 = MX ? kSfbCol + 8 : kAccCols;                 // first A slot
-  constexpr int kACols = MX ? KS / 4 + 8 : KS / 2;                    // columns of one A slot (fp8: 64 of values + 8 of scale factors)
-  constexpr int kAStages = (kTmemCols - kSlot0) / kACols;             // lone CTA: 8, 6, 3 (fp8: 5); pair: 6, 3
+  constexpr int kACols = W4 ? 8 : (MX ? KS / 4 + 8 : KS / 2);         // columns of one A slot (fp8: 64 of values + 8 of scale factors; fp4: the scale factors only)
+  constexpr int kSfCol = W4 ? 0 : KS / 4;                             // scale-factor columns inside an fp8 / fp4 slot
+  constexpr int kAStages = W4 ? kMaxAStages : (kTmemCols - kSlot0) / kACols;   // lone CTA: 8, 6, 3 (fp8: 6); pair: 6, 3
   constexpr int kSubPerW = kWStageK / KS;                             // stages per packed-weight stage
   constexpr int kPieces = KS / 64;                                    // 64-K pieces of a stage
   static_assert(kAStages <= kMaxAStages, "A ring too deep for the barrier arrays");
@@ -570,7 +629,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // barrier per stage.
   constexpr bool kMerged = CTAS == 2;
   constexpr int kMxSplit = 1;   // fp8 form: dequant warps per lane quarter sharing one stage
-  constexpr int kDequantSets = dequant_sets(CTAS, MX != 0), kEpiSets = epi_sets(CTAS);
+  constexpr int kDequantSets = dequant_sets(CTAS, MX != 0, W4), kEpiSets = epi_sets(CTAS);
   constexpr int kEpiWarp0 = 4 + 4 * kDequantSets;   // first epilogue warp
   static_assert((kEpiWarp0 + 4 * kEpiSets) * 32 == kThreads, "the role split must use every warp");
   const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
@@ -580,14 +639,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* w_smem = smem;                                      // w_stages x 16 KB
-  uint8_t* b_smem = w_smem + p.w_stages * kWStageBytes;        // b_stages x b_stage_bytes
+  uint8_t* b_smem = w_smem + p.w_stages * kWBytes;             // b_stages x b_stage_bytes
   uint8_t* sc_smem = b_smem + p.b_stages * p.b_stage_bytes;    // scale_bufs x scale_buf_bytes
   Barriers* bars = reinterpret_cast<Barriers*>(sc_smem + p.scale_bufs * p.scale_buf_bytes);
   // gate/up epilogue staging: 2 x (32 tokens x 64 features) bf16, 16-byte aligned
   uint16_t* epi_stage = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(Barriers) + 127) & ~size_t(127)));
   constexpr bool kUseLut = CTAS == 1 && !MX;
   uint32_t* lut = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(epi_stage) +
-                                              (GATEUP ? kEpiStageBytes : kEpiStageDownBytes));
+                                              epi_stage_bytes(GATEUP, CTAS));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &bars->abort_flag;
@@ -596,7 +655,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
   if (tid == 0) {
     for (int i = 0; i < kMaxWStages; ++i) {
       mbar_init(smem_u32(&bars->w_full[i]), 1);
-      mbar_init(smem_u32(&bars->w_empty[i]), MX ? 4 * kMxSplit : 4 * kDequantSets);   // fp8 form: only the owning team reads a stage
+      // fp8 form: only the owning team reads a stage; fp4 form: the stage's MMAs release it
+      mbar_init(smem_u32(&bars->w_empty[i]), W4 ? 1 : (MX ? 4 * kMxSplit : 4 * kDequantSets));
     }
     for (int i = 0; i < kMaxAStages; ++i) {
       mbar_init(smem_u32(&bars->a_full[i]), kMerged ? 4 * CTAS + 1 : (MX ? 4 * kMxSplit : 4));
@@ -608,7 +668,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(smem_u32(&bars->sc_empty[i]), 4 * kDequantSets);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bars->acc_full[i]), 1);
+      mbar_init(smem_u32(&bars->acc_full[i]), (W4 && p.K > KS) ? 2 : 1);   // one commit per issuing warp that has a stage
       mbar_init(smem_u32(&bars->acc_empty[i]), 4 * kEpiSets * CTAS);
     }
     bars->abort_flag = 0;
@@ -654,7 +714,37 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // ------------------- TMA producer: packed weights + scales ---------------
     // Runs ahead by the depth of its own ring, independent of the token stages,
     // so the weight stream (the HBM-bound part) is never held back by them.
-    if (lane == 0) {
+    if (W4) {
+      // Prepacked-fp4 form: ONE copy per stage - a 5-D box (K inside a 128-K half, 8 rows, 2 row
+      // groups, 8 groups of 16 accumulator rows, 2 halves) lands the item's 128 rows x 256 K in
+      // accumulator row order. Issuing a copy costs the issuing thread a hundred cycles or
+      // more, which is why a stage is not split into several.
+      if (lane == 0) {
+        Ring w;
+        bool ok = true;
+        for (int item = unit; item < n_items && ok; item += n_units) {
+          const TokTile tt = p.tiles[item / n_fgroups];
+          const int f = item_f(item);
+          const int g0 = GATEUP ? (tt.expert * n_wrows + f * 64) >> 3 : (tt.expert * n_wrows + f * 128) >> 4;
+          for (int kw = 0; kw < n_kw; ++kw) {
+            if (!mbar_wait(smem_u32(&bars->w_empty[w.slot]), w.phase ^ 1u, abort_flag, 2)) {
+              ok = false;
+              break;
+            }
+            const uint32_t bar = smem_u32(&bars->w_full[w.slot]);
+            const uint32_t dst = smem_u32(w_smem + w.slot * kWBytes);
+            if (p.K - kw * kWStageK > 128) {
+              mbar_expect_tx(bar, kW4TileBytes);   // the copy counts packed bytes: half of what it writes
+              tma_load_5d(dst, &tmap_w, 0, 0, 0, g0, 2 * kw, bar);
+            } else {   // K ends inside the stage's first half: the 4-D map of single halves (in the tmap_b64 slot)
+              mbar_expect_tx(bar, kW4TileBytes / 2);
+              tma_load_4d(dst, &tmap_b64, kw * kWStageK, 0, 0, g0, bar);
+            }
+            w.advance(p.w_stages);
+          }
+        }
+      }
+    } else if (lane == 0) {
       Ring w;
       uint32_t sc_it = 0;
       bool ok = true;
@@ -816,8 +906,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (W4 && warp == 3)) {
     // ------------------------------ MMA issuer -----------------------------
+    const int iss = W4 && warp == 3 ? 1 : 0;   // prepacked-fp4 form: second issuing warp, odd stages
     // The whole warp stays converged: lanes 0 and 1 poll the A-ready and the
     // tokens-ready barrier of the stage in the SAME instruction (one poll latency
     // instead of two), lane 0 issues the MMAs and one commit per stage.
@@ -884,19 +975,27 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         acc_phase ^= 1u;
       }
     }
-    Ring a, b;
+    Ring a, b, wr;   // wr: the weight ring, read by the MMAs of the prepacked-fp4 form only
     int acc_it = 0;
     for (int item = unit; item < n_items && ok && !kMerged; item += n_units, ++acc_it) {
       const int n_rows_u = __shfl_sync(0xFFFFFFFFu, p.tiles[item / n_fgroups].n_rows, 0);
-      const uint32_t idesc = MX ? make_idesc_mx(2 * n_rows_u) : make_idesc(n_rows_u);
+      const uint32_t idesc = MX ? make_idesc_mx(2 * n_rows_u, W4 ? 5u : 1u) : make_idesc(n_rows_u);
       const int ab = acc_it % kAccBufs;
-      const uint32_t d_addr = tmem_u + ab * kAccCols;
+      const uint32_t d_addr = tmem_u + ab * kAccCols + iss * kAccCols;
       if (!mbar_wait(smem_u32(&bars->acc_empty[ab]), (((uint32_t)(acc_it / kAccBufs)) & 1u) ^ 1u, abort_flag, 4)) break;
       tc_fence_after();
       for (int st = 0; st < n_stages; ++st) {
-        const uint32_t bar = lane == 0 ? smem_u32(&bars->a_full[a.slot]) : smem_u32(&bars->b_full[b.slot]);
-        const uint32_t par = lane == 0 ? a.phase : b.phase;
-        if (!mbar_wait_lanes(bar, par, lane < 2, abort_flag, 5)) {
+        if (kIssuers == 2 && (st & 1) != iss) {   // the other warp's stage
+          a.advance(kAStages);
+          b.advance(p.b_stages);
+          wr.advance(p.w_stages);
+          continue;
+        }
+        const uint32_t first = st >= kIssuers ? 1u : 0u;   // 0 in this warp's first stage of the item
+        const uint32_t bar = lane == 0 ? smem_u32(&bars->a_full[a.slot])
+                                       : (lane == 1 ? smem_u32(&bars->b_full[b.slot]) : smem_u32(&bars->w_full[wr.slot]));
+        const uint32_t par = lane == 0 ? a.phase : (lane == 1 ? b.phase : wr.phase);
+        if (!mbar_wait_lanes(bar, par, lane < (W4 ? 3 : 2), abort_flag, 5)) {
           ok = false;
           break;
         }
@@ -911,10 +1010,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const int n_kb = min(8, (p.K - st * KS) / 32);
 #pragma unroll
             for (int kb = 0; kb < 8; ++kb) {
-              if (kb < n_kb)
-                tc_mma_mx(d_addr, a_addr + kb * 8, desc0 + (kb >> 2) * 2 * slice16 + (kb & 3) * 2,
-                          idesc | ((uint32_t)(kb & 3) << 29), a_addr + KS / 4 + (kb >> 2) * 4, tmem_u + kSfbCol,
-                          (st | kb) != 0 ? 1u : 0u);
+              if (kb < n_kb) {
+                const uint64_t bdesc = desc0 + (kb >> 2) * 2 * slice16 + (kb & 3) * 2;
+                const uint32_t id = idesc | ((uint32_t)(kb & 3) << 29), sfa = a_addr + kSfCol + (kb >> 2) * 4;
+                if (W4) {
+                  // the block's 32 container bytes of every weight row in the stage's shared-memory tile
+                  const uint64_t adesc = make_b_desc(smem_u32(w_smem + wr.slot * kWBytes)) +
+                                         (uint64_t)((kb >> 2) * (kW4TileBytes >> 4) + (kb & 3) * 2);
+                  tc_mma_mx_ss(d_addr, adesc, bdesc, id, sfa, tmem_u + kSfbCol, (first | kb) != 0 ? 1u : 0u);
+                } else {
+                  tc_mma_mx(d_addr, a_addr + kb * 8, bdesc, id, sfa, tmem_u + kSfbCol, (first | kb) != 0 ? 1u : 0u);
+                }
+              }
             }
           } else {
             const int n_slices = min(kPieces, (p.K - st * KS) / 64);
@@ -929,11 +1036,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
           }
           tc_commit(smem_u32(&bars->stage_done[a.slot]));
-          if (st == n_stages - 1) tc_commit(smem_u32(&bars->acc_full[ab]));
+          if (W4) tc_commit(smem_u32(&bars->w_empty[wr.slot]));   // the MMAs were the stage's last readers
+          if (st + kIssuers >= n_stages) tc_commit(smem_u32(&bars->acc_full[ab]));   // this warp's last stage of the item
         }
         __syncwarp();
         a.advance(kAStages);
         b.advance(p.b_stages);
+        if (W4) wr.advance(p.w_stages);
       }
     }
   } else if (warp >= 4 && warp < kEpiWarp0) {
@@ -974,7 +1083,75 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         pending = -1;
       }
     };
-    if (MX) {
+    if (W4) {
+      // Prepacked-fp4 form: nothing to expand. Per stage the four warps put the scale factors
+      // (sanitised and laid out [stage][accumulator row][8 groups] by the prepack) into the
+      // stage's scale-factor columns: column 4 h + i, byte b = tensor-memory row 32 i + lane,
+      // group 4 h + b; every lane quarter keeps a full copy. They are read straight from global
+      // memory into registers one stage ahead of their use, and one lane pulls them into L2
+      // kW4Ahead stages ahead of that (a kilobyte a stage), so the register loads hit L2: a
+      // load that went to HBM would take longer than a stage lasts and pace the whole pipeline.
+      // (Pulling the WEIGHT stages into L2 ahead of the ring the same way was measured: no gain.)
+      Ring sa;
+      auto item_sf = [&](int item) {
+        const TokTile tt = p.tiles[item / n_fgroups];
+        return p.w_scale + ((size_t)tt.expert * p.n_ftiles + item_f(item)) * n_kw * kW4SfBytes;
+      };
+      // cursor of the L2 prefetch (first warp, lane 0) and of the register prefetch (everyone)
+      int pf_item = unit, pf_kw = 0;
+      const uint8_t* pf_sf = nullptr;
+      constexpr int kW4Ahead = 6;
+      auto prefetch_stage = [&]() {
+        if (pf_item >= n_items) return;
+        if (pf_kw == 0) pf_sf = item_sf(pf_item);
+        bulk_prefetch_l2(pf_sf + (size_t)pf_kw * kW4SfBytes, kW4SfBytes);
+        if (++pf_kw == n_kw) {
+          pf_kw = 0;
+          pf_item += n_units;
+        }
+      };
+      const bool pf_lane = warp == 4 && lane == 0;
+      if (pf_lane)
+        for (int i = 0; i < kW4Ahead; ++i) prefetch_stage();
+      int nx_item = unit, nx_kw = 0;
+      const uint8_t* nx_sf = nx_item < n_items ? item_sf(nx_item) : nullptr;
+      uint2 nxt[4];
+      auto load_next = [&]() {
+        if (nx_item >= n_items) return;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          nxt[i] = __ldg(reinterpret_cast<const uint2*>(nx_sf + (size_t)nx_kw * kW4SfBytes + (32 * i + lane) * 8));
+        if (++nx_kw == n_kw) {
+          nx_kw = 0;
+          nx_item += n_units;
+          if (nx_item < n_items) nx_sf = item_sf(nx_item);
+        }
+      };
+      load_next();
+      for (int item = unit; item < n_items && ok; item += n_units) {
+        for (int kw = 0; kw < n_kw; ++kw) {
+          uint32_t sf[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            sf[i] = nxt[i].x;
+            sf[4 + i] = nxt[i].y;
+          }
+          load_next();
+          if (pf_lane) prefetch_stage();
+          if (!mbar_wait(smem_u32(&bars->stage_done[sa.slot]), sa.phase ^ 1u, abort_flag, 9)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          tc_st8(t_row + sa.slot * kACols, sf);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[sa.slot]));
+          sa.advance(kAStages);
+        }
+      }
+    } else if (MX) {
       // fp8 form. A team (one warp per tensor-memory lane quarter) takes every kTeams-th stage of
       // this CTA's running stage sequence (items follow each other without a gap in it); a warp
       // expands its 32 rows of the stage in two halves of 128 K, each with the scale factors of
@@ -1075,7 +1252,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 tc_st16(slot_col + pc * 16, v);
               }
             }
-            tc_st4(slot_col + KS / 4 + 4 * half, sf[0], sf[1], sf[2], sf[3]);
+            tc_st4(slot_col + kSfCol + 4 * half, sf[0], sf[1], sf[2], sf[3]);
           }
           tc_wait_st();
           tc_fence_before();
@@ -1192,7 +1369,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           bars->tile_ref[j] = real ? reinterpret_cast<unsigned long long>(orow) : 0ull;
         }
         if (!GATEUP) bars->tile_w[j] = (real && p.topk_w != nullptr) ? p.topk_w[p.w_sorted ? tt.row0 + j : flat] : 0.0f;
-        if (MX) bars->tile_s[j] = real ? p.tok_scale[tt.row0 + j] : 0.0f;
+        // (prepacked fp4: the codes read as twice the table value)
+        if (MX) bars->tile_s[j] = real ? p.tok_scale[tt.row0 + j] * (W4 ? 0.5f : 1.0f) : 0.0f;
       }
       // The wait's outcome is shared by all epilogue warps before anyone acts on it: a warp that
       // gave up must not leave the others standing at a later named barrier.
@@ -1230,14 +1408,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
           tc_ld_16x256b_x4(t_lane + c0, va);
           tc_ld_16x256b_x4(t_lane + (16u << 16) + c0, vb);
           if (MX) {   // the second piece's partial products sit n_rows columns further on
-            uint32_t wa[16], wb[16];
-            tc_ld_16x256b_x4(t_lane + tt.n_rows + c0, wa);
-            tc_ld_16x256b_x4(t_lane + (16u << 16) + tt.n_rows + c0, wb);
-            tc_wait_ld();
+            // (fp4 form: and the second issuing warp's accumulator kAccCols further on, if K gave it a stage)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              va[i] = __float_as_uint(__uint_as_float(va[i]) + __uint_as_float(wa[i]));
-              vb[i] = __float_as_uint(__uint_as_float(vb[i]) + __uint_as_float(wb[i]));
+            for (int extra = 1; extra < 2 * kIssuers; ++extra) {
+              if (extra >= 2 && p.K <= KS) break;
+              const uint32_t off = (uint32_t)((extra & 1) * tt.n_rows + (extra >> 1) * kAccCols);
+              uint32_t wa[16], wb[16];
+              tc_ld_16x256b_x4(t_lane + off + c0, wa);
+              tc_ld_16x256b_x4(t_lane + (16u << 16) + off + c0, wb);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                va[i] = __float_as_uint(__uint_as_float(va[i]) + __uint_as_float(wa[i]));
+                vb[i] = __float_as_uint(__uint_as_float(vb[i]) + __uint_as_float(wb[i]));
+              }
             }
           }
           tc_wait_ld();
@@ -1316,11 +1500,15 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             uint32_t v[32];
             tc_ld32(t_lane + c0, v);
             if (MX) {   // the second piece's partial products sit n_rows columns further on
-              uint32_t v2[32];
-              tc_ld32(t_lane + tt.n_rows + c0, v2);
-              tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+              for (int extra = 1; extra < 2 * kIssuers; ++extra) {
+                if (extra >= 2 && p.K <= KS) break;
+                uint32_t v2[32];
+                tc_ld32(t_lane + (uint32_t)((extra & 1) * tt.n_rows + (extra >> 1) * kAccCols) + c0, v2);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+              }
             }
             tc_wait_ld();
             if (c0 + 32 * kEpiSets >= tt.n_rows) release_acc();   // this warp's last read of the accumulator
@@ -1373,11 +1561,15 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             uint32_t v[32];
             tc_ld32(t_lane + c0, v);
             if (MX) {
-              uint32_t v2[32];
-              tc_ld32(t_lane + tt.n_rows + c0, v2);
-              tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+              for (int extra = 1; extra < 2 * kIssuers; ++extra) {
+                if (extra >= 2 && p.K <= KS) break;
+                uint32_t v2[32];
+                tc_ld32(t_lane + (uint32_t)((extra & 1) * tt.n_rows + (extra >> 1) * kAccCols) + c0, v2);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+              }
             }
             tc_wait_ld();
             if (c0 + 32 >= tt.n_rows) release_acc();
@@ -1682,6 +1874,60 @@ combine_rows_kernel(const float* __restrict__ partial, const float* __restrict__
 }
 
 // ---------------------------------------------------------------------------
+// prepack: checkpoint-layout MXFP4 -> the form the prepacked-fp4 GEMM reads
+// ---------------------------------------------------------------------------
+// Codes. The layer's table {0, .25, 1, 1.5, 2, 3} (magnitude codes 0..5) times two is
+// {0, .5, 2, 3, 4, 6}: e2m1 codes 0, 1, 4, 5, 6, 7 - every code from 2 on moves up by two. Codes
+// 6 and 7 (inf, NaN in this layer) have no e2m1 counterpart: they are counted, and a caller
+// that finds a non-zero count keeps such weights on the checkpoint-layout path. A group whose
+// scale byte is 0xFF (zero weights in this layer, NaN to the tensor core) becomes zero codes.
+// One thread per 32-element group (16 bytes).
+__global__ void prepack_codes_kernel(const uint4* __restrict__ w, const uint8_t* __restrict__ scale, long long n_groups,
+                                     uint4* __restrict__ out, int* __restrict__ nonfinite) {
+  const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_groups) return;
+  uint4 v = w[g];
+  uint32_t x[4] = {v.x, v.y, v.z, v.w}, bad = 0u;
+  const bool zero = scale[g] == 0xFFu;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t b1 = x[i] >> 1, b2 = x[i] >> 2;
+    bad |= b1 & b2 & 0x11111111u;
+    x[i] = zero ? 0u : x[i] + (((b1 | b2) & 0x11111111u) << 1);
+  }
+  if (bad != 0u && !zero) atomicAdd(nonfinite, 1);
+  out[g] = make_uint4(x[0], x[1], x[2], x[3]);
+}
+
+// Scale factors, regrouped per (expert, 128-row work item, 256-K stage) as [128 accumulator
+// rows][8 groups] so that a stage's kilobyte is one contiguous copy; rows and groups past the
+// end read as 1.0 (0x7F), and so does the 0xFF of a zeroed group. One thread per byte.
+__global__ void prepack_scales_kernel(const uint8_t* __restrict__ scale, int gateup, int n_feat, int K, int n_ftiles,
+                                      int n_kw, long long total, uint8_t* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int b = (int)(i & 7), L = (int)((i >> 3) & 127);
+  long long r = i >> 10;
+  const int kw = (int)(r % n_kw);  r /= n_kw;
+  const int f = (int)(r % n_ftiles);
+  const long long e = r / n_ftiles;
+  const int kb = kw * 8 + b, pitch = K / 32;
+  long long row = -1;
+  if (gateup) {
+    const int sr = ((L >> 3) & 1) * 64 + (L >> 4) * 8 + (L & 7);   // accumulator row -> staged row (gate rows, then up rows)
+    row = e * 2 * n_feat + (sr < 64 ? f * 64 + sr : n_feat + f * 64 + sr - 64);
+  } else if (f * 128 + L < n_feat) {
+    row = e * n_feat + f * 128 + L;
+  }
+  uint8_t v = 0x7Fu;
+  if (row >= 0 && kb < pitch) {
+    v = scale[row * pitch + kb];
+    if (v == 0xFFu) v = 0x7Fu;
+  }
+  out[i] = v;
+}
+
+// ---------------------------------------------------------------------------
 // host side: tensor maps, workspace layout, launch
 // ---------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1735,6 +1981,41 @@ CUtensorMap make_map(const void* ptr, CUtensorMapDataType dt, int elem_bytes, ui
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  if (cache.size() >= 64) cache.erase(cache.begin());
+  cache.emplace_back(key, m);
+  return m;
+}
+
+// Prepacked fp4 weights [rows, K / 2] as the copy engine's packed-4-bit type that pads every 16
+// nibbles to 16 bytes in shared memory. Four dimensions so that ONE box lands the 128 rows of a
+// work item in accumulator row order 16 g + 8 u + j:
+//   gate/up: j = feature inside a group of 8, u = gate / up half (n_feat rows apart), g = group;
+//   down:    plain row order (u = 8 rows apart, g = 16 rows apart).
+// and a fifth dimension counts the 128-K halves of a row, so that one box = one 256-K stage.
+// The type wants an inner box of exactly 128 elements and 32-byte strides (K a multiple of 64);
+// a row's last stage may read on into the next row: those columns meet zero-filled token columns.
+// `half`: the 4-D map whose box is ONE 128-K half (for a last stage that K ends in early).
+CUtensorMap make_map_w4(const void* ptr, int K, bool gateup, int n_feat, bool half = false) {
+  static std::mutex mu;
+  static std::vector<std::pair<MapKey, CUtensorMap>> cache;
+  const MapKey key{ptr, (uint64_t)K, (uint64_t)n_feat, (uint64_t)K / 2, half ? 64u : 128u, gateup ? 1u : 2u,
+                   (int)CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B};
+  std::lock_guard<std::mutex> lock(mu);
+  for (auto& kv : cache)
+    if (kv.first == key) return kv.second;
+  expects((reinterpret_cast<uintptr_t>(ptr) & 31u) == 0 && K % 64 == 0, "prepacked weights: 32-byte alignment, K a multiple of 64");
+  CUtensorMap m;
+  const uint64_t pitch = (uint64_t)K / 2;
+  const cuuint64_t n_halves = (cuuint64_t)((K + kWStageK - 1) / kWStageK) * 2;   // whole stages: the tail reads on into the next row
+  const cuuint64_t dims[5] = {half ? n_halves * 128 : 128, 8, 2, (cuuint64_t)1 << 27, n_halves};
+  const cuuint64_t strides[4] = {pitch, gateup ? (cuuint64_t)n_feat * pitch : 8 * pitch, gateup ? 8 * pitch : 16 * pitch, 64};
+  const cuuint32_t box[5] = {128, 8, 2, 8, 2};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, half ? 4 : 5, const_cast<void*>(ptr), dims, strides, box,
+                                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled (packed 4-bit) failed with code " + std::to_string((int)r));
   if (cache.size() >= 64) cache.erase(cache.begin());
   cache.emplace_back(key, m);
   return m;
@@ -1798,7 +2079,7 @@ bool pair_fits(const GemmParams& p, bool gateup) {
   return 227 * 1024 - fixed - scale_tile - tokens >= 2 * kWStageBytes;
 }
 
-template <bool GATEUP, int KS, int CTAS, int MX = 0>
+template <bool GATEUP, int KS, int CTAS, int MX = 0, bool W4 = false>
 void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
                     cudaStream_t stream) {
   // Shared memory: token stages (this CTA's rows x KS), scales (double-buffered when they fit),
@@ -1806,47 +2087,51 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   // 16 KB): the deeper it is, the more weight bytes are in flight, which is what a decode-size
   // batch is bound by.
   constexpr int kAccCols = acc_cols(KS, CTAS);
-  constexpr int kAStages = MX ? (kTmemCols - 2 * MX - 8) / (KS / 4 + 8) : (kTmemCols - kAccCols) / (KS / 2);
-  constexpr int kThreads = block_threads(CTAS, MX != 0);
+  constexpr int kAStages = W4 ? kMaxAStages : (MX ? (kTmemCols - 2 * MX - 8) / (KS / 4 + 8) : (kTmemCols - kAccCols) / (KS / 2));
+  constexpr int kThreads = block_threads(CTAS, MX != 0, W4);
+  constexpr int kWBytes = W4 ? kW4StageBytes : kWStageBytes;
   const int max_smem = 227 * 1024;
-  const int scale_tile = (128 * (p.K / 32) + 127) & ~127;
-  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + (GATEUP ? kEpiStageBytes : kEpiStageDownBytes) + 128 +
+  // (the prepacked-fp4 form carries each stage's scale factors in the weight ring)
+  const int scale_tile = W4 ? 0 : (128 * (p.K / 32) + 127) & ~127;
+  const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + epi_stage_bytes(GATEUP, CTAS) + 128 +
                     (CTAS == 1 && !MX ? kLutBytes : 0);
   // a pair's MMA N is the tile rounded up to 32 rows, half of them staged by each CTA
   p.b_stage_bytes = (CTAS == 2 ? (((p.max_tok + 31) >> 5) << 4) : p.max_tok) * 128 * (KS / 64);
   // token ring: 4 slots for a lone CTA; a pair has one token slot per A slot
   // (the fp8 form: token tiles are small - 8 KB a stage at 16 rows - but come a stage at a time
   // from L2 with its full latency, so their ring is as deep as the A ring allows)
-  int b_stages = CTAS == 2 ? kAStages : (MX ? (p.max_tok <= 16 ? 6 : 4) : (kAStages < 4 ? kAStages : 4)), scale_bufs = 2;
+  // (prepacked fp4: five token slots and four weight slots measured best at 32-row tiles - the
+  // token ring, fed from L2 a stage at a time, is the one that must not run dry)
+  int b_stages = CTAS == 2 ? kAStages : (MX ? (p.max_tok <= 16 ? 6 : (W4 ? 5 : 4)) : (kAStages < 4 ? kAStages : 4)), scale_bufs = 2;
   auto w_room = [&]() {
-    return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWStageBytes;
+    return (max_smem - fixed - scale_bufs * scale_tile - b_stages * p.b_stage_bytes) / kWBytes;
   };
   if (w_room() < 4) scale_bufs = 1;
-  while (CTAS == 1 && w_room() < 3 && b_stages > 2) --b_stages;
+  while (CTAS == 1 && w_room() < (W4 ? 4 : 3) && b_stages > 2) --b_stages;
   expects(w_room() >= 2, "fused_moe_mxfp4: reduction dimension too large for shared memory");
   p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
   if (CTAS == 1 && p.w_stages == kMaxWStages) {   // spare room: deepen the token ring
     const int keep_w = kMaxWStages;
     while (b_stages < kAStages && b_stages < kMaxBStages &&
-           (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWStageBytes >= keep_w)
+           (max_smem - fixed - scale_bufs * scale_tile - (b_stages + 1) * p.b_stage_bytes) / kWBytes >= keep_w)
       ++b_stages;
     p.w_stages = w_room() > kMaxWStages ? kMaxWStages : w_room();
   }
   p.b_stages = b_stages;
   p.scale_bufs = scale_bufs;
   p.scale_buf_bytes = scale_tile;
-  const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWStageBytes;
+  const int smem = fixed + scale_bufs * scale_tile + b_stages * p.b_stage_bytes + p.w_stages * kWBytes;
   // the attribute belongs to the device's context: once per device and instantiation
   static std::atomic<bool> configured[64];
   int dev = 0;
   VK_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !configured[dev].load()) {
-    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX>,
+    VK_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX, W4>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     if (dev >= 0 && dev < 64) configured[dev].store(true);
   }
   if (CTAS == 1) {
-    moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
+    moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX, W4><<<sm_count(), kThreads, smem, stream>>>(tw, tb, tb64, p);
   } else {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(sm_count() & ~1));
@@ -1860,15 +2145,18 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    VK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX>, tw, tb, tb64, p));
+    VK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_gemm_sm100_kernel<GATEUP, KS, CTAS, MX, W4>, tw, tb, tb64, p));
   }
 }
 
 // Stage length and CTA grouping by the largest token tile of the launch (see the kernel's comment).
 template <bool GATEUP>
 void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap& tb64, GemmParams p,
-                 bool use_pair, cudaStream_t stream, bool mx = false) {
-  if (p.max_tok <= 32 && mx) launch_gemm_ks<GATEUP, 256, 1, 32>(tw, tb, tb64, p, stream);
+                 bool use_pair, cudaStream_t stream, bool mx = false, bool w4 = false) {
+  if (w4) {
+    expects(p.max_tok <= 32 && mx, "prepacked fp4 weights serve token tiles of up to 32 rows");
+    launch_gemm_ks<GATEUP, 256, 1, 32, true>(tw, tb, tb64, p, stream);
+  } else if (p.max_tok <= 32 && mx) launch_gemm_ks<GATEUP, 256, 1, 32>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 64) launch_gemm_ks<GATEUP, 256, 1>(tw, tb, tb64, p, stream);
   else if (p.max_tok <= 128) launch_gemm_ks<GATEUP, 128, 1>(tw, tb, tb64, p, stream);
   else if (use_pair) launch_gemm_ks<GATEUP, 128, 2>(tw, tb, tb64, p, stream);
@@ -1879,6 +2167,44 @@ void launch_gemm(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensorMap
 
 size_t sm100_workspace_bytes(int EM, int hidden, int ispp) { return ws_layout(EM, hidden, ispp).total; }
 size_t sm100_workspace_bytes_ordered(int EM, int hidden, int ispp, int N) { return ws_layout(EM, hidden, ispp, true, N).total; }
+
+// Sizes of the prepacked form of one weight set. which = 0: w13 [E, 2 * ispp, hidden / 2];
+// 1: w2 [E, hidden, ispp / 2]. The code buffer carries 128 rows + 64 bytes of zero padding: a
+// work item's box always spans 128 rows and a row's last 128-K box may reach past the row.
+void prepack_sizes(int which, int E, int hidden, int ispp, size_t* w_bytes, size_t* sf_bytes) {
+  expects(which == 0 || which == 1, "prepack: which must be 0 (w13) or 1 (w2)");
+  expects(E > 0 && hidden > 0 && ispp > 0 && hidden % 64 == 0 && ispp % 64 == 0, "prepack: hidden and ispp must be multiples of 64");
+  const long long rows = which == 0 ? 2ll * ispp : hidden;
+  const int K = which == 0 ? hidden : ispp;
+  const int n_ftiles = which == 0 ? ispp / 64 : (hidden + 127) / 128;
+  const int n_kw = (K + kWStageK - 1) / kWStageK;
+  if (w_bytes) *w_bytes = (size_t)(E * rows + 128) * (K / 2) + 256;
+  if (sf_bytes) *sf_bytes = (size_t)E * n_ftiles * n_kw * kW4SfBytes;
+}
+
+void prepack_weights(int which, const uint8_t* w, const uint8_t* scale, int E, int hidden, int ispp, uint8_t* w_out,
+                     uint8_t* sf_out, int* nonfinite, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  size_t w_bytes = 0, sf_bytes = 0;
+  prepack_sizes(which, E, hidden, ispp, &w_bytes, &sf_bytes);
+  expects(w && scale && w_out && sf_out && nonfinite, "prepack: buffers must not be null");
+  auto aligned = [](const void* p, unsigned a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+  expects(aligned(w, 16) && aligned(w_out, 32) && aligned(sf_out, 16), "prepack: w 16-byte, w_out 32-byte, sf_out 16-byte aligned");
+  const long long rows = which == 0 ? 2ll * ispp : hidden;
+  const int K = which == 0 ? hidden : ispp;
+  const int n_feat = which == 0 ? ispp : hidden;
+  const int n_ftiles = which == 0 ? ispp / 64 : (hidden + 127) / 128;
+  const int n_kw = (K + kWStageK - 1) / kWStageK;
+  const long long n_groups = (long long)E * rows * (K / 32);
+  VK_CUDA_CHECK(cudaMemsetAsync(nonfinite, 0, sizeof(int), stream));
+  VK_CUDA_CHECK(cudaMemsetAsync(w_out + (size_t)n_groups * 16, 0, w_bytes - (size_t)n_groups * 16, stream));
+  prepack_codes_kernel<<<(unsigned)((n_groups + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(w), scale, n_groups, reinterpret_cast<uint4*>(w_out), nonfinite);
+  const long long total = (long long)sf_bytes;
+  prepack_scales_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scale, which == 0 ? 1 : 0, n_feat, K, n_ftiles,
+                                                                           n_kw, total, sf_out);
+  VK_CUDA_CHECK(cudaGetLastError());
+}
 // ---------------------------------------------------------------------------
 // optional per-kernel timing: CUDA events recorded around the two GEMM kernels
 // on the launch stream (no synchronisation while recording), summed on demand.
@@ -2003,7 +2329,7 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                       int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM,
                       float swiglu_limit, int activation, float beta, float linear_beta,
                       const float* b13, const float* b2, int block_size, cudaStream_t stream,
-                      const RowPtrs* rows, uint16_t* y_bf16) {
+                      const RowPtrs* rows, uint16_t* y_bf16, bool w4) {
   const bool store_rows = rows != nullptr && rows->store_slots;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   const uint16_t* const* a_rows = rows ? rows->a_rows : nullptr;
@@ -2026,8 +2352,10 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   // cover the rows of every expert id that fits an int32 row index.
   const uint64_t w13_rows_cap = (uint64_t)1 << 31;
   const TileChoice choice = choose_tiles(M, top_k, EM, block_size, hidden, ispp);
-  const bool mx = choice.max_tok <= 64 && small_fp8_mode();
+  const bool mx = choice.max_tok <= 64 && (small_fp8_mode() || w4);
   const int max_tok = mx ? std::min(choice.max_tok, 32) : choice.max_tok;   // the fp8 form takes tiles of up to 32 rows
+  expects(!w4 || mx, "fused_moe_mxfp4: prepacked weights serve decode-size batches only (token tiles of up to 64 rows); "
+                     "larger batches take the checkpoint-layout weights");
   const bool use_pair = choice.use_pair;
   // a small problem's tile list is built by an extra CTA of the row pre-pass (one launch less)
   const bool tiles_in_split = mx && EM / block_size <= 1024;
@@ -2066,12 +2394,13 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
     GemmParams p = g;
     p.w_scale = w13_scale; p.bias = b13; p.act = act_scratch; p.tok_scale = scale_x;
     p.K = hidden; p.n_feat = ispp; p.n_ftiles = ispp / 64;
-    const CUtensorMap tw = make_map(w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, hidden / 2,
-                                    w13_rows_cap, hidden / 2, 128, 64);
+    const CUtensorMap tw = w4 ? make_map_w4(w13, hidden, true, ispp)
+                              : make_map(w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, hidden / 2, w13_rows_cap, hidden / 2, 128, 64);
     CUtensorMap tb, tb64;
     token_maps(mx ? static_cast<const void*>(x8) : static_cast<const void*>(gathered), hidden, tb, tb64);
+    if (w4) tb64 = make_map_w4(w13, hidden, true, ispp, true);
     timer_mark(0, stream);
-    launch_gemm<true>(tw, tb, tb64, p, use_pair, stream, mx);
+    launch_gemm<true>(tw, tb, tb64, p, use_pair, stream, mx, w4);
     timer_mark(1, stream);
   }
   if (mx)
@@ -2087,11 +2416,12 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
       p.raw = partial;
       p.raw_ld = hidden;
     }
-    const CUtensorMap tw = make_map(w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ispp / 2, w13_rows_cap,
-                                    ispp / 2, 128, 64);
+    const CUtensorMap tw = w4 ? make_map_w4(w2, ispp, false, hidden)
+                              : make_map(w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ispp / 2, w13_rows_cap, ispp / 2, 128, 64);
     CUtensorMap tb, tb64;
     token_maps(mx ? static_cast<const void*>(a8) : static_cast<const void*>(act_scratch), ispp, tb, tb64);
-    launch_gemm<false>(tw, tb, tb64, p, use_pair, stream, mx);
+    if (w4) tb64 = make_map_w4(w2, ispp, false, hidden, true);
+    launch_gemm<false>(tw, tb, tb64, p, use_pair, stream, mx, w4);
     timer_mark(2, stream);
   }
   if (ordered)

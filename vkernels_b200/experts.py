@@ -86,7 +86,12 @@ class FusedMoEMxfp4:
                  scaling: float = 1.0, n_group: int = 1, topk_group: int = 1, n_shared: int = 0,
                  swiglu_limit: float = 0.0, activation: int = ops.moe_fused_mxfp4.SWIGLU,
                  beta: float = 4.0, linear_beta: float = 25.0, b13=None, b2=None,
-                 max_tokens: int = DEFAULT_TOKEN_BUDGET, block_size: int = 16):
+                 max_tokens: int = DEFAULT_TOKEN_BUDGET, block_size: int = 16, prepack: bool = False):
+        """``prepack``: also keep the weights in the prepacked form (``ops.prepack_weights``; about as
+        large as the checkpoint form again) and run decode-size batches from it - their kernels
+        then expand nothing and run at the memory rate. Off by default because of the memory; a
+        weight set with codes the form cannot express (inf / NaN) silently stays on the
+        checkpoint layout (``self.prepacked`` is None then)."""
         ops.same_gpu_contiguous(w13, w13_scale, w2, w2_scale)
         self.w13, self.w13_scale, self.w2, self.w2_scale = w13, w13_scale, w2, w2_scale
         self.b13, self.b2 = b13, b2
@@ -109,6 +114,10 @@ class FusedMoEMxfp4:
         self.block_size = block_size
         self.max_tokens = int(max_tokens or DEFAULT_TOKEN_BUDGET)
         self.capture_stream = None
+        self.prepacked = None
+        if prepack:
+            packed = ops.prepack_weights(w13, w13_scale, w2, w2_scale)
+            self.prepacked = packed if packed.usable else None
         self._reserve()
 
     # -- sizing ------------------------------------------------------------------------------
@@ -196,12 +205,15 @@ class FusedMoEMxfp4:
                     out=(bufs["sids"], bufs["eids"], bufs["out_em"]))
         if not return_fp32 and T <= self.ORDERED_COMBINE_TOKENS:
             y = bufs["y"].view(T, self.hidden) if out_bf16 is None else out_bf16
+            kw = dict(top_k=topk_ids.shape[1], block_size=self.block_size, swiglu_limit=self.swiglu_limit,
+                      activation=self.activation, beta=self.beta, linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
             with _region("moe:apply.launch"):
-                ops.fused_moe_mxfp4_bf16_into(y, bufs["act"], x, self.w13, self.w13_scale, self.w2, self.w2_scale,
-                                              topk_w.reshape(-1), sids, eids, top_k=topk_ids.shape[1],
-                                              block_size=self.block_size, swiglu_limit=self.swiglu_limit,
-                                              activation=self.activation, beta=self.beta,
-                                              linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+                if self.prepacked is not None:
+                    ops.fused_moe_mxfp4_bf16_prepacked_into(y, bufs["act"], x, self.prepacked, topk_w.reshape(-1), sids,
+                                                            eids, **kw)
+                else:
+                    ops.fused_moe_mxfp4_bf16_into(y, bufs["act"], x, self.w13, self.w13_scale, self.w2, self.w2_scale,
+                                                  topk_w.reshape(-1), sids, eids, **kw)
             return y
         out = bufs["out"].view(T, self.hidden)
         with _region("moe:apply.launch"):
@@ -344,11 +356,11 @@ class HostPipeline:
         self.d2h.synchronize()
 
 
-def layer_from_config(cfg, weights: dict, router: dict | None, *, max_tokens: int | None = None):
+def layer_from_config(cfg, weights: dict, router: dict | None, *, max_tokens: int | None = None, prepack: bool = False):
     """Build the layer for a ``synthetic.MoEConfig`` from generated tensors."""
     return FusedMoEMxfp4(
         weights["w13"], weights["w13_scale"], weights["w2"], weights["w2_scale"], top_k=cfg.top_k,
         router_weight=None if router is None else router["wr"],
         router_bias=None if router is None else router["bias"], routing=cfg.routing,
         renorm=cfg.renorm, scaling=cfg.scaling, n_group=cfg.n_group, topk_group=cfg.topk_group,
-        n_shared=cfg.shared_experts, swiglu_limit=cfg.swiglu_limit, max_tokens=max_tokens)
+        n_shared=cfg.shared_experts, swiglu_limit=cfg.swiglu_limit, max_tokens=max_tokens, prepack=prepack)

@@ -45,6 +45,11 @@ _SIGNATURES = {
     "vk_cuda_fused_moe_mxfp4_bf16": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
                                      [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_cuda_moe_workspace_bytes_bf16": (c_size_t, [c_int] * 5),
+    "vk_cuda_moe_prepack_sizes": (c_int, [c_int] * 4 + [c_void_p] * 2),
+    "vk_cuda_moe_prepack_weights": (c_int, [c_int] + [c_void_p] * 2 + [c_int] * 3 + [c_void_p] * 4),
+    "vk_cuda_fused_moe_mxfp4_bf16_prepacked": (c_int, [c_void_p] * 8 + [c_int] * 4 + [c_void_p] * 2 +
+                                               [c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_int,
+                                                c_void_p]),
     "vk_cuda_moe_router_logits": (c_int, [c_void_p] * 3 + [c_int] * 3 + [c_void_p]),
     "vk_cuda_moe_route_topk": (c_int, [c_void_p] * 2 + [c_int] * 7 + [c_float, c_int] + [c_void_p] * 3),
     "vk_cuda_moe_route_align_small": (c_int, [c_void_p] * 2 + [c_int] * 7 + [c_float] + [c_int] * 3 + [c_void_p] * 6),

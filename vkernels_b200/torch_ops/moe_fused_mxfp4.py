@@ -265,6 +265,79 @@ def fused_moe_mxfp4_bf16_into(y_bf16, act_scratch, hidden_states, w13, w13_scale
     return y_bf16
 
 
+class PrepackedWeights:
+    """Both weight sets of a layer in the prepacked form of ``vk_cuda_moe_prepack_weights`` plus
+    the shapes they were made from. ``nonfinite`` is the number of 32-element groups that hold a
+    code this form cannot express (inf / NaN in the layer's table); when it is not zero the
+    object must not be used (``usable`` is False) and the checkpoint-layout weights stay in charge."""
+
+    def __init__(self, w13_codes, w13_sf, w2_codes, w2_sf, E, hidden, ispp, nonfinite):
+        self.w13_codes, self.w13_sf, self.w2_codes, self.w2_sf = w13_codes, w13_sf, w2_codes, w2_sf
+        self.E, self.hidden, self.ispp, self.nonfinite = E, hidden, ispp, nonfinite
+
+    @property
+    def usable(self) -> bool:
+        return self.nonfinite == 0
+
+
+def prepack_weights(w13, w13_scale, w2, w2_scale) -> PrepackedWeights:
+    """One-time rewrite of checkpoint-layout MXFP4 weights into the form the decode kernels read
+    without expanding anything (see ``vk_cuda_moe_prepack_weights``). Allocates the two code
+    buffers (checkpoint size + padding) and the regrouped scales; reads back one int."""
+    import ctypes
+
+    require(w13.dtype == torch.uint8 and w13.dim() == 3 and w2.dtype == torch.uint8 and w2.dim() == 3,
+            "w13 / w2 must be uint8 [E, rows, K/2]")
+    same_gpu_contiguous(w13, w13_scale, w2, w2_scale)
+    E, two_i, half_h = w13.shape
+    ispp, hidden = two_i // 2, half_h * 2
+    require(tuple(w2.shape) == (E, hidden, ispp // 2), "w2 must be [E, hidden, ispp/2]")
+    require(tuple(w13_scale.shape) == (E, two_i, hidden // 32) and tuple(w2_scale.shape) == (E, hidden, ispp // 32),
+            "scales must be [E, rows, K/32]")
+    lib = nr.load_library()
+    out, bad = [], torch.zeros(2, dtype=torch.int32, device=w13.device)
+    with torch.cuda.device(w13.device):
+        for which, (w, sc) in enumerate(((w13, w13_scale), (w2, w2_scale))):
+            wb, sb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+            nr.check(lib.vk_cuda_moe_prepack_sizes(which, E, hidden, ispp, ctypes.addressof(wb), ctypes.addressof(sb)),
+                     "moe_prepack_sizes")
+            codes = torch.empty(wb.value, dtype=torch.uint8, device=w13.device)
+            sf = torch.empty(sb.value, dtype=torch.uint8, device=w13.device)
+            nr.check(lib.vk_cuda_moe_prepack_weights(which, _ptr(w), _ptr(sc), E, hidden, ispp, _ptr(codes), _ptr(sf),
+                                                     bad.data_ptr() + 4 * which, _stream(w13)), "moe_prepack_weights")
+            out += [codes, sf]
+    return PrepackedWeights(out[0], out[1], out[2], out[3], E, hidden, ispp, int(bad.sum().item()))
+
+
+def fused_moe_mxfp4_bf16_prepacked_into(y_bf16, act_scratch, hidden_states, packed: PrepackedWeights, topk_weights,
+                                        sorted_ids, expert_ids, *, top_k: int, block_size: int = 16,
+                                        swiglu_limit: float = 0.0, activation: int = SWIGLU, beta: float = 4.0,
+                                        linear_beta: float = 25.0, b13=None, b2=None):
+    """``fused_moe_mxfp4_bf16_into`` on prepacked weights: decode-size batches only (the library
+    refuses a batch whose token tiles would exceed 64 rows; M <= 256 never does)."""
+    require(packed.usable, "these weights hold codes the prepacked form cannot express; use the checkpoint layout")
+    M, hidden = hidden_states.shape
+    ispp = packed.ispp
+    require(hidden == packed.hidden and hidden_states.dtype == torch.bfloat16, "hidden_states must be bf16 [M, hidden]")
+    same_gpu_contiguous(hidden_states, packed.w13_codes, packed.w13_sf, packed.w2_codes, packed.w2_sf, topk_weights,
+                        sorted_ids, expert_ids, y_bf16, act_scratch, *[t for t in (b13, b2) if t is not None])
+    for b, cols, name in ((b13, 2 * ispp, "b13"), (b2, hidden, "b2")):
+        require(b is None or (b.dtype == torch.float32 and tuple(b.shape) == (packed.E, cols)), f"{name} must be fp32 [E, {cols}]")
+    EM = sorted_ids.numel()
+    require(EM % block_size == 0 and expert_ids.numel() * block_size >= EM, "sorted_ids / expert_ids do not match block_size")
+    require(y_bf16.dtype == torch.bfloat16 and y_bf16.numel() >= M * hidden, "y must be bf16 [M, hidden]")
+    require(act_scratch.dtype == torch.bfloat16 and act_scratch.numel() >= EM * ispp, "act_scratch must be bf16 [EM, ispp]")
+    require(topk_weights.dtype == torch.float32 and topk_weights.numel() >= M * top_k, "topk_weights too small")
+    with torch.cuda.device(hidden_states.device):
+        rc = nr.load_library().vk_cuda_fused_moe_mxfp4_bf16_prepacked(
+            _ptr(hidden_states), _ptr(packed.w13_codes), _ptr(packed.w13_sf), _ptr(packed.w2_codes), _ptr(packed.w2_sf),
+            _ptr(topk_weights), _ptr(act_scratch), _ptr(y_bf16), M, hidden, ispp, top_k, _ptr(sorted_ids),
+            _ptr(expert_ids), EM, float(swiglu_limit), int(activation), float(beta), float(linear_beta), _ptr(b13),
+            _ptr(b2), block_size, _stream(hidden_states))
+    nr.check(rc, "fused_moe_mxfp4_bf16_prepacked")
+    return y_bf16
+
+
 def fused_moe_mxfp4_rows_into(act_scratch, a_rows, out_rows, w13, w13_scale, w2, w2_scale, topk_weights,
                               sorted_ids, expert_ids, *, top_k: int, block_size: int = 16,
                               swiglu_limit: float = 0.0, activation: int = SWIGLU, beta: float = 4.0,
