@@ -87,5 +87,14 @@ def test_experts_apply_matches_the_oracle():
         torch.cuda.synchronize()
         ref = oracle_layer(A, w, torch.from_numpy(ids_np), tw, swiglu_limit=0.7, b13=to_np(b13c), b2=to_np(b2c))
         assert_close_bf16(to_np(out.float()), ref, "experts.apply", got_is_bf16=True)
+    # the same call served from weights prepacked on first use
+    exp = B200FusedExperts(w13_scale=s13, w2_scale=s2, w13_bias=b13c, w2_bias=b2c, swiglu_limit=0.7, max_num_tokens=128,
+                           prepack=True)
+    for _ in range(2):
+        out.zero_()
+        exp.apply(out, A, w13, w2, tw, ids, activation="swigluoai", global_num_experts=cfg.E, workspace13=ws13)
+        torch.cuda.synchronize()
+        assert exp._packed is not None and exp._packed.usable
+        assert_close_bf16(to_np(out.float()), ref, "experts.apply, prepacked", got_is_bf16=True)
     with pytest.raises(OpNotEligible):
         ex.apply(out, A, w13, w2, tw, ids, activation="gelu", global_num_experts=cfg.E)

@@ -74,7 +74,12 @@ class B200FusedExperts:
     buffer of this object sized at ``max_num_tokens`` and never reallocated afterwards."""
 
     def __init__(self, *, w13_scale, w2_scale, w13_bias=None, w2_bias=None, swiglu_limit: float = 0.0,
-                 beta: float = 4.0, linear_beta: float = 25.0, max_num_tokens: int = 8192):
+                 beta: float = 4.0, linear_beta: float = 25.0, max_num_tokens: int = 8192, prepack: bool = False):
+        """``prepack``: on the first decode-size call (M <= 256) rewrite the weights once into the
+        form the decode kernels read without expanding anything (``ops.prepack_weights``; costs a
+        second copy of the weights) and serve such calls from it. Weights that hold the layer's
+        inf / NaN codes stay on the checkpoint layout."""
+        self.prepack, self._packed, self._packed_key = prepack, None, None
         self.w13_scale, self.w2_scale, self.b13, self.b2 = w13_scale, w2_scale, w13_bias, w2_bias
         self.swiglu_limit, self.beta, self.linear_beta = swiglu_limit, beta, linear_beta
         self.max_num_tokens = max_num_tokens
@@ -124,9 +129,18 @@ class B200FusedExperts:
             act = self._act[: em * ispp]
         y = output if output.dtype == torch.bfloat16 and output.is_contiguous() else \
             torch.empty((M, hidden), dtype=torch.bfloat16, device=hidden_states.device)
-        ops.fused_moe_mxfp4_bf16_into(y, act, hidden_states, w1, self.w13_scale, w2, self.w2_scale,
-                                      topk_weights.to(torch.float32).reshape(-1).contiguous(), sids, eids, top_k=top_k,
-                                      block_size=bs, swiglu_limit=self.swiglu_limit, activation=act_kind, beta=self.beta,
-                                      linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+        kw = dict(top_k=top_k, block_size=bs, swiglu_limit=self.swiglu_limit, activation=act_kind, beta=self.beta,
+                  linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
+        tw = topk_weights.to(torch.float32).reshape(-1).contiguous()
+        packed = None
+        if self.prepack and M <= 256:
+            key = (w1.data_ptr(), w2.data_ptr())
+            if self._packed_key != key:      # first decode-size call (or the weights moved): rewrite once
+                self._packed, self._packed_key = ops.prepack_weights(w1, self.w13_scale, w2, self.w2_scale), key
+            packed = self._packed if self._packed.usable else None
+        if packed is not None:
+            ops.fused_moe_mxfp4_bf16_prepacked_into(y, act, hidden_states, packed, tw, sids, eids, **kw)
+        else:
+            ops.fused_moe_mxfp4_bf16_into(y, act, hidden_states, w1, self.w13_scale, w2, self.w2_scale, tw, sids, eids, **kw)
         if y is not output:
             output.copy_(y)
