@@ -302,6 +302,43 @@ def test_bf16_form_with_ordered_combine(name, T):
     assert_close_bf16(got if tokens is None else got[tokens], ref, f"bf16 form {name} T={T}", got_is_bf16=True)
 
 
+@pytest.mark.parametrize("name,T", [("c0", 1), ("c0", 6), ("c1", 1), ("c1", 2), ("c1", 3), ("c3_small", 1), ("c4", 2)])
+def test_flat_form_for_a_handful_of_slots(name, T):
+    """Up to twelve routed slots the bf16 entry point runs two flat kernels (moe_gemv.cu) instead
+    of the grouped GEMMs: against the oracle, against the fp32 form, bit-reproducible, with
+    biases, with a slot whose expert is not local (id -1) and with a 0xFF scale group."""
+    # c3_small: the sigmoid / group-limited router with its always-on shared expert (8 + 1 slots), at a size the oracle likes
+    cfg = syn.scaled(syn.CONFIGS["c3"], H=1024, I=512, E=32) if name == "c3_small" else syn.CONFIGS[name]
+    w, A, r = make_case(cfg, T, backend="torch")
+    w["w13_scale"][0, 3, 1] = 0xFF
+    logits = syn.make_zipf_logits(cfg, T, device=DEV) if cfg.zipf_alpha else None
+    ids_np, tw_np, _ = oracle_route(cfg, A, r, logits=None if logits is None else to_np(logits))
+    assert ids_np.size <= 12
+    if name == "c1" and T == 3:
+        ids_np = ids_np.copy()
+        ids_np[1, 2] = -1                       # a slot some other rank owns
+    ids, tw = torch.from_numpy(ids_np).to(DEV), torch.from_numpy(tw_np).to(DEV)
+    E = w["w13"].shape[0]
+    rng = np.random.default_rng(T + 11)
+    b13 = torch.from_numpy(rng.standard_normal((E, 2 * cfg.I)).astype(np.float32) * 0.1).to(DEV)
+    b2 = torch.from_numpy(rng.standard_normal((E, cfg.H)).astype(np.float32) * 0.1).to(DEV)
+    sids, eids, _ = ops.moe_align_block_size(ids, E, 16)
+    act = torch.zeros((sids.numel(), cfg.I), dtype=torch.bfloat16, device=DEV)
+    kw = dict(top_k=ids.shape[1], swiglu_limit=cfg.swiglu_limit, b13=b13, b2=b2)
+    ys = []
+    for _ in range(2):
+        y = torch.full((T, cfg.H), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.fused_moe_mxfp4_bf16_into(y, act, A, w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], tw.reshape(-1).contiguous(),
+                                      sids, eids, **kw)
+        torch.cuda.synchronize()
+        ys.append(y.clone())
+    assert torch.equal(ys[0], ys[1])
+    ref = oracle_layer(A, w, ids, tw, swiglu_limit=cfg.swiglu_limit, b13=to_np(b13), b2=to_np(b2))
+    assert_close_bf16(to_np(ys[0].float()), ref, f"flat form {name} T={T}", got_is_bf16=True)
+    base = gpu_layer(A, w, ids, tw, impl="tcgen05", swiglu_limit=cfg.swiglu_limit, b13=b13, b2=b2)
+    assert_close_bf16(to_np(ys[0].float()), to_np(base), f"flat form vs fp32 form {name} T={T}", got_is_bf16=True)
+
+
 def _ocp_decode(codes_u8, K):
     """Prepacked code bytes [rows, K/2] -> values as the tensor core reads e2m1, halved."""
     ocp = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)

@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "_build")
 LIB_PATH = os.path.join(HERE, "lib", "libvkernels_b200.so")
-SOURCES = ["moe_fused.cu", "moe_align.cu", "moe_route.cu", "moe_simt.cu", "moe_gemm_sm100.cu",
+SOURCES = ["moe_fused.cu", "moe_align.cu", "moe_route.cu", "moe_simt.cu", "moe_gemm_sm100.cu", "moe_gemv.cu",
            "moe_ep.cu", "moe_stages.cu", "capi.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",

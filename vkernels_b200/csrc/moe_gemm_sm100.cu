@@ -2091,7 +2091,7 @@ void launch_gemm_ks(const CUtensorMap& tw, const CUtensorMap& tb, const CUtensor
   constexpr int kThreads = block_threads(CTAS, MX != 0, W4);
   constexpr int kWBytes = W4 ? kW4StageBytes : kWStageBytes;
   const int max_smem = 227 * 1024;
-  // (the prepacked-fp4 form carries each stage's scale factors in the weight ring)
+  // (the prepacked-fp4 form reads its scale factors straight from global memory: no tile of them)
   const int scale_tile = W4 ? 0 : (128 * (p.K / 32) + 127) & ~127;
   const int fixed = 1024 + (((int)sizeof(Barriers) + 127) & ~127) + epi_stage_bytes(GATEUP, CTAS) + 128 +
                     (CTAS == 1 && !MX ? kLutBytes : 0);
@@ -2323,6 +2323,14 @@ TileChoice choose_tiles(int M, int top_k, int EM, int block_size, int k_gateup, 
 }
 }  // namespace
 
+// moe_gemv.cu
+bool moe_tiny_eligible(int M, int hidden, int ispp, int top_k);
+void launch_moe_tiny(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+                     const uint8_t* w2_scale, const float* topk_w, uint16_t* act, uint16_t* y, int M, int hidden, int ispp,
+                     int top_k, const int32_t* sorted_ids, const int32_t* expert_ids, int EM, float swiglu_limit,
+                     int activation, float beta, float linear_beta, const float* b13, const float* b2, int block_size,
+                     int32_t* slot_expert, cudaStream_t stream);
+
 void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_scale,
                       const uint8_t* w2, const uint8_t* w2_scale, const float* topk_w,
                       int w_sorted, uint16_t* act_scratch, float* out, int M, int hidden, int ispp,
@@ -2347,6 +2355,17 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
   uint16_t* gathered = reinterpret_cast<uint16_t*>(ws + l.gathered_off);
   int32_t* inv = ordered ? reinterpret_cast<int32_t*>(ws + l.inv_off) : nullptr;
   float* partial = ordered ? reinterpret_cast<float*>(ws + l.partial_off) : nullptr;
+
+  // One or two decode tokens: two flat kernels instead of the grouped GEMMs and their helpers.
+  if (ordered && rows == nullptr && !w4 && w_sorted == 0 && moe_tiny_eligible(M, hidden, ispp, top_k)) {
+    timer_mark(0, stream);
+    launch_moe_tiny(A, w13, w13_scale, w2, w2_scale, topk_w, act_scratch, y_bf16, M, hidden, ispp, top_k, sorted_ids,
+                    expert_ids, EM, swiglu_limit, activation, beta, linear_beta, b13, b2, block_size,
+                    reinterpret_cast<int32_t*>(ws + l.count_off + 64), stream);
+    timer_mark(1, stream);
+    timer_mark(2, stream);
+    return;
+  }
 
   // The number of experts is not an argument of the layer; the tensor maps
   // cover the rows of every expert id that fits an int32 row index.

@@ -127,6 +127,7 @@ class FusedMoEMxfp4:
     # Batches up to this many tokens take the bf16-output form of the layer: ordered combine, no
     # fp32 output buffer to zero and convert (two launches less per step, bit-reproducible).
     ORDERED_COMBINE_TOKENS = 256
+    TINY_SLOTS = 12
 
     def _workspace_bytes(self) -> int:
         T = self.max_tokens
@@ -208,7 +209,8 @@ class FusedMoEMxfp4:
             kw = dict(top_k=topk_ids.shape[1], block_size=self.block_size, swiglu_limit=self.swiglu_limit,
                       activation=self.activation, beta=self.beta, linear_beta=self.linear_beta, b13=self.b13, b2=self.b2)
             with _region("moe:apply.launch"):
-                if self.prepacked is not None:
+                # (up to twelve routed slots the library runs two flat kernels on the checkpoint layout)
+                if self.prepacked is not None and T * topk_ids.shape[1] > self.TINY_SLOTS:
                     ops.fused_moe_mxfp4_bf16_prepacked_into(y, bufs["act"], x, self.prepacked, topk_w.reshape(-1), sids,
                                                             eids, **kw)
                 else:
