@@ -1091,7 +1091,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
       // memory into registers one stage ahead of their use, and one lane pulls them into L2
       // kW4Ahead stages ahead of that (a kilobyte a stage), so the register loads hit L2: a
       // load that went to HBM would take longer than a stage lasts and pace the whole pipeline.
-      // (Pulling the WEIGHT stages into L2 ahead of the ring the same way was measured: no gain.)
+      // (Pulling the WEIGHT stages into L2 ahead of the ring was measured too: a tensor-map
+      // prefetch per stage changes nothing, one 128-byte bulk prefetch per row and stage from
+      // these 128 threads doubles the kernel's time.)
       Ring sa;
       auto item_sf = [&](int item) {
         const TokTile tt = p.tiles[item / n_fgroups];
