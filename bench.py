@@ -455,13 +455,27 @@ def run_single_gpu(args, cfg, T):
             pipe.submit(xhs[i & 1], yhs[i & 1])
         pipe.drain()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        # the same loop in steady state: from the arrival of the last warm-up step's result on the host to the
+        # arrival of the K-th timed one (no drain in between, so no pipeline fill and drain inside the K steps)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(max(args.warmup, 2)):
+            pipe.submit(xhs[i & 1], yhs[i & 1])
+        ev0.record(pipe.d2h)
+        for i in range(args.steps):
+            pipe.submit(xhs[i & 1], yhs[i & 1])
+        ev1.record(pipe.d2h)
+        pipe.drain()
+        steady_ms = ev0.elapsed_time(ev1) / args.steps
         yh = yhs[(args.steps - 1) & 1]
         e2e_dev = yh.to(dev)
         e2e_par = oracle_parity(cfg, A, e2e_dev, ids0, tw0, w, min(args.parity_tokens, 32), cfg.seed + 1)
         e2e = {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.H * 2,
                "d2h_bytes_per_step": T * cfg.H * 2, "ms_per_step": e2e_ms, "ms_per_step_serial": serial_ms,
+               "ms_per_step_steady_state": steady_ms,
                "how": "HostPipeline: every step copies its batch in from pinned memory and its result out; the copies "
-                      "of neighbouring steps overlap the layer on separate streams",
+                      "of neighbouring steps overlap the layer on separate streams; value / ms_per_step: K steps from an idle "
+                      "pipeline to the last result on the host (fill and drain included); ms_per_step_steady_state: "
+                      "result-to-result time of K steps inside a running pipeline",
                "parity": {k: e2e_par[k] for k in ("tokens", "max_abs", "rel_l2", "ok")}}
         if not e2e_par["ok"]:
             print(json.dumps({"error": "end-to-end output differs from the CPU oracle", "parity": e2e_par}), flush=True)
