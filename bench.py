@@ -513,12 +513,26 @@ def run_multi_gpu(args, cfg, T):
     dist.init_process_group("nccl", device_id=torch.device(dev))
     T_global = T * world if args.weak else T
     T_local = T_global // world
-    layer = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T_local)
+    sl = slice(rank * T_local, (rank + 1) * T_local)
+    A_full = syn.make_activations(cfg, T_global, backend="torch", device=dev, seed=cfg.seed)
+    lg_full = syn.make_zipf_logits(cfg, T_global, device=dev) if cfg.zipf_alpha else None
+    order = None
+    if args.placement == "balanced":
+        # experts renumbered so that the contiguous plan's ranks carry even loads: the load is measured on this
+        # very batch (every rank computes the same global routing, so all arrive at the same numbering)
+        from vkernels_b200.dist import balanced_expert_order
+
+        scores = lg_full if lg_full is not None else A_full.float() @ syn.make_router(cfg, device=dev)["wr"].t()
+        load = torch.bincount(scores.topk(cfg.top_k, dim=1).indices.flatten(), minlength=cfg.E)
+        order = balanced_expert_order(load.cpu().tolist(), world)
+        if lg_full is not None:
+            lg_full = lg_full[:, torch.tensor(order, device=dev)].contiguous()
+    layer = ExpertParallelMoE.from_config(cfg, rank=rank, world=world, device=dev, max_tokens=T_local, expert_order=order)
     if os.environ.get("VK_EP_FORM", "peer") == "peer":
         layer.enable_peer_memory(T_local)   # falls back to the collective form when unavailable
-    sl = slice(rank * T_local, (rank + 1) * T_local)
-    A = syn.make_activations(cfg, T_global, backend="torch", device=dev, seed=cfg.seed)[sl].contiguous()
-    logits = syn.make_zipf_logits(cfg, T_global, device=dev)[sl].contiguous() if cfg.zipf_alpha else None
+    A = A_full[sl].contiguous()
+    logits = lg_full[sl].contiguous() if lg_full is not None else None
+    del A_full, lg_full
     if layer._peer is not None:
         # inputs resident in HBM means: resident in the rank's registered activation buffer, which the
         # owners of the experts read in place
@@ -539,9 +553,15 @@ def run_multi_gpu(args, cfg, T):
         ids0 = torch.cat([ids0, torch.full((T_local, 1), cfg.E, dtype=torch.int32, device=dev)], 1)
         tw0 = torch.cat([tw0, torch.ones((T_local, 1), dtype=torch.float32, device=dev)], 1)
     full_w = syn.make_expert_weights(cfg, backend="torch", device=dev)
+    router_full = syn.make_router(cfg, device=dev)
+    if order is not None:      # the checker sees the same renumbering as the layer
+        oi = torch.tensor(order + list(range(cfg.E, cfg.n_weight_experts)), device=dev)
+        full_w = {k: v.index_select(0, oi) for k, v in full_w.items()}
+        ro = torch.tensor(order, device=dev)
+        router_full = {k: (None if v is None else v.index_select(0, ro).contiguous()) for k, v in router_full.items()}
     # (the ranks share the host's cores: each takes its share of the threads and a smaller sample)
     par = oracle_parity(cfg, A, y0, ids0.contiguous(), tw0.contiguous(), full_w, min(args.parity_tokens, max(8, 64 // world)),
-                        cfg.seed + rank, logits=logits, router=syn.make_router(cfg, device=dev),
+                        cfg.seed + rank, logits=logits, router=router_full,
                         threads=max(1, (os.cpu_count() or 1) // world))
     del full_w
     torch.cuda.empty_cache()
@@ -584,6 +604,7 @@ def run_multi_gpu(args, cfg, T):
     eager_step()
     stats = layer.last_stats()
     stats["launch"] = "CUDA graph replay" if y_graph is not None else "eager"
+    stats["placement"] = "experts renumbered by measured load (balanced_expert_order)" if order is not None else "contiguous"
     layer.count_local_slots = False
     layer.time_phases = False
     # load per rank: expert slots each rank computed in that step, slowest rank's phases
@@ -661,6 +682,9 @@ def main():
                     help="profiling runs only: no oracle check and no end-to-end leg (single GPU)")
     ap.add_argument("--prepack", action="store_true",
                     help="single GPU, batches up to 256 tokens: run from weights prepacked at load (the decode sweep always does)")
+    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
+                    help="multi-GPU: contiguous expert ranges in the checkpoint's numbering (the reference plan), or experts "
+                         "renumbered by measured load first")
     ap.add_argument("--weak", action="store_true", help="multi-GPU: keep the batch PER RANK fixed (weak scaling)")
     ap.add_argument("--no-decode-sweep", dest="decode_sweep", action="store_false")
     args = ap.parse_args()

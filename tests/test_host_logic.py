@@ -129,3 +129,26 @@ def test_zipf_logits_make_a_hot_expert():
     top = np.argsort(-logits, axis=1)[:, :4]
     share = np.bincount(top.ravel(), minlength=cfg.E).max() / 4096
     assert share > 0.20   # the hottest expert receives more than 20 % of the tokens
+
+
+def test_balanced_expert_order_evens_out_a_zipf_load():
+    """balanced_expert_order: a permutation that keeps every rank's share of experts and brings
+    the heaviest rank's load under the contiguous plan's, down to the floor a single dominant
+    expert sets."""
+    from vkernels_b200.dist import balanced_expert_order, ep_plan
+
+    rng = np.random.default_rng(5)
+    E = 128
+    load = (20000.0 / np.arange(1, E + 1) ** 1.2)[rng.permutation(E)]
+    for world in (2, 4, 8, 3):
+        order = balanced_expert_order(load.tolist(), world)
+        assert sorted(order) == list(range(E))
+        def rank_loads(numbering):
+            return [sum(load[numbering[i]] for i in range(*ep_plan(E, world, r))) for r in range(world)]
+        before, after = rank_loads(list(range(E))), rank_loads(order)
+        assert max(after) <= max(before) + 1e-9
+        floor = max(load.max(), load.sum() / world)
+        assert max(after) <= 1.15 * floor, (world, max(after), floor)
+        for r in range(world):     # inside a rank the experts stay in ascending order
+            b, e = ep_plan(E, world, r)
+            assert order[b:e] == sorted(order[b:e])

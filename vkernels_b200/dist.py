@@ -43,6 +43,27 @@ import torch.distributed as dist
 from . import native_runtime as nr
 
 
+def balanced_expert_order(load, world: int):
+    """Expert numbering that evens out the ranks' load under the contiguous plan of ``ep_plan``:
+    experts are dealt to the ranks heaviest first, each to the rank with the least load so far that
+    still has room (every rank keeps exactly its ``ep_plan`` share), and the result lists rank 0's
+    experts (ascending), then rank 1's, and so on. ``load``: slots per expert measured on a
+    representative batch. Returns a list ``order`` with ``order[new_id] = old_id``. The reference
+    plan (src/c/vkernels/dist/dist_moe.cpp:225-260) is contiguous in the checkpoint's numbering;
+    renumbering the experts (weights and router rows together) keeps that plan and its dispatch
+    unchanged. One expert heavier than a rank's fair share still sets the floor: replication is
+    not built."""
+    E = len(load)
+    sizes = [ep_plan(E, world, r)[1] - ep_plan(E, world, r)[0] for r in range(world)]
+    members = [[] for _ in range(world)]
+    total = [0.0] * world
+    for e in sorted(range(E), key=lambda i: (-float(load[i]), i)):
+        r = min((r for r in range(world) if len(members[r]) < sizes[r]), key=lambda r: (total[r], r))
+        members[r].append(e)
+        total[r] += float(load[e])
+    return [e for r in range(world) for e in sorted(members[r])]
+
+
 def ep_plan(num_experts: int, ep: int, rank: int) -> tuple[int, int]:
     """[begin, end) of the experts owned by `rank` (dist_moe.cpp:225-240)."""
     if ep <= 0 or not (0 <= rank < ep) or num_experts < ep:
@@ -237,20 +258,32 @@ class ExpertParallelMoE:
         self._last_routing = None        # (ids, w) of the most recent call (views of layer buffers)
 
     @classmethod
-    def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None):
-        """Generates this rank's slice of the seeded weights of a benchmark configuration."""
+    def from_config(cls, cfg, *, rank, world, device, max_tokens, group=None, seed=None, expert_order=None):
+        """Generates this rank's slice of the seeded weights of a benchmark configuration.
+        ``expert_order`` (see ``balanced_expert_order``): position p of the layer's expert numbering
+        holds expert ``expert_order[p]`` of the configuration - weights and router rows alike, so
+        the layer is the same function with its experts renumbered, and the contiguous ranges of
+        the plan become whatever sets the order groups together."""
         from . import synthetic as syn
         from .experts import FusedMoEMxfp4
 
         b, e = ep_plan(cfg.E, world, rank)
         # every rank draws the same stream and keeps its slice (+ the shared experts)
         full = syn.make_expert_weights(cfg, seed=seed, backend="torch", device=device)
-        keep = list(range(b, e)) + list(range(cfg.E, cfg.n_weight_experts))
+        order = list(range(cfg.E)) if expert_order is None else [int(v) for v in expert_order]
+        if sorted(order) != list(range(cfg.E)):
+            raise ValueError("expert_order must be a permutation of the routed experts")
+        if expert_order is not None and cfg.n_group != 1:
+            raise ValueError("group-limited routing depends on the experts' numbering: no renumbering for it")
+        keep = order[b:e] + list(range(cfg.E, cfg.n_weight_experts))
         idx = torch.tensor(keep, device=device)
         w = {k: v.index_select(0, idx).contiguous() for k, v in full.items()}
         del full
         torch.cuda.empty_cache()
         r = syn.make_router(cfg, seed=seed, device=device)
+        if expert_order is not None:
+            oi = torch.tensor(order, device=device)
+            r = {k: (None if v is None else v.index_select(0, oi).contiguous()) for k, v in r.items()}
         local = FusedMoEMxfp4(w["w13"], w["w13_scale"], w["w2"], w["w2_scale"], top_k=cfg.top_k,
                               router_weight=r["wr"], router_bias=r["bias"], routing=cfg.routing,
                               renorm=cfg.renorm, scaling=cfg.scaling, n_group=cfg.n_group,
