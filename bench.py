@@ -307,10 +307,16 @@ def kernel_times(fn, calls):
 GATEUP_DRAM_BYTES = {("c2_gptoss120b_prefill", 8192): 1.503e9}
 
 
-def launches_per_step(T, slots):
-    """Kernels of this library per layer call: router logits + top-k, alignment (1 kernel up to
-    1024 routed slots, else 3), tile list, row gather, gate/up GEMM, down GEMM."""
-    return 2 + (1 if T * slots <= 1024 else 3) + 4
+def launches_per_step(T, slots, H=2880):
+    """Kernels of this library per layer call: router logits (prefill sizes: weight split, tcgen05
+    GEMM, and the sum of its K-slice planes when the batch is cut into slices) + top-k, alignment
+    (1 kernel up to 1024 routed slots, else 3), tile list, row gather, gate/up GEMM, down GEMM."""
+    router = 1
+    if T > 512:
+        tiles = (T + 127) // 128
+        z = max(1, min(8, (H // 64) // 4, torch.cuda.get_device_properties(0).multi_processor_count // tiles))
+        router = 2 + (1 if z > 1 else 0)
+    return router + 1 + (1 if T * slots <= 1024 else 3) + 4
 
 
 def decode_sweep(peaks, steps, warmup, prepack=True, parity_tokens=8):
@@ -489,7 +495,7 @@ def run_single_gpu(args, cfg, T):
             "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32", "data": "synthetic",
             "config": workload_config(cfg, T, 1), "roofline": roofline, "parity": parity,
             "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}, "e2e": e2e,
-            "gpu_launches": launches_per_step(T, cfg.slots) * args.steps, "clocks": clocks}
+            "gpu_launches": launches_per_step(T, cfg.slots, cfg.H) * args.steps, "clocks": clocks}
     if args.decode_sweep:
         del layer, w
         torch.cuda.empty_cache()

@@ -2265,6 +2265,18 @@ void timer_mark(int which, cudaStream_t stream) {
 }  // namespace
 
 
+// For the other tcgen05 kernel of the library (the router GEMM, moe_route.cu): a bf16 tensor map
+// [outer, inner] with a byte pitch and a 128-byte-wide box, and the device address of the
+// status word, so that its bounded waits report through the same word.
+CUtensorMap sm100_make_map_bf16(const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_outer) {
+  return make_map(ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, inner, outer, pitch_bytes, 64, box_outer);
+}
+int* sm100_status_address() {
+  int* p = nullptr;
+  VK_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_kernel_status));
+  return p;
+}
+
 // Status of the tcgen05 launches on the current device since the last reset: 0, or
 // 100 + the code of the wait that ran out. Synchronises the device.
 int sm100_last_status() {

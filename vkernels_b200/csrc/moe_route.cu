@@ -10,8 +10,12 @@
 // rule used is the DeepSeek-V3 one: a group's score is the sum of its two
 // largest biased scores and only experts of the topk_group best groups stay
 // eligible.
+#include <cuda.h>
+
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
+#include <string>
 #include "common.cuh"
 #include "moe_fused.hpp"
 #include "moe_prep.cuh"
@@ -242,6 +246,226 @@ router_logits_mma_kernel(const uint16_t* __restrict__ x, const float* __restrict
   }
 }
 
+// ---------------------------------------------------------------------------
+// Router logits on tcgen05 (prefill-size batches).
+//
+// D[128 tokens, E experts] = x[128, K] . (hi + mid + lo)[E, K]^T with the fp32 router weight
+// split once per call into three bf16 terms (exact: hi + mid + lo == w). One CTA per 128-token
+// tile and K slice: a TMA producer warp streams the token tile and the three weight-term tiles
+// of each 64-K chunk through a shared-memory ring (128-byte swizzle), one thread issues twelve
+// kind::f16 MMAs per chunk (A and B both from shared memory), four warps read the accumulators
+// back and store the rows.
+//
+// The tensor core adds a product to its fp32 accumulator by truncating the addend to the
+// accumulator's last bit (measured: adding 0.75 ulp sixty-four times changes nothing), so every
+// MMA into a large accumulator costs up to one ulp of it. Hence TWO accumulators: the hi term
+// into one (one truncation per 16 K), the mid and lo terms - 2^-8 and 2^-16 of the size, so
+// their truncations are that much smaller in absolute terms - into the other; the epilogue
+// adds the two in fp32. That leaves K / 16 truncations of at most one ulp with the sign of
+// the addend, a random walk about as long as the rounding noise of a sequential fp32 sum over
+// K terms - the yardstick the routing parity tests hold the logits to.
+// ---------------------------------------------------------------------------
+namespace tc {
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait (about two seconds of SM clock); false when it ran out or another role gave up.
+__device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > 4000000000ll) {
+        *abort_flag = code;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {   // K-major tile of 128-byte rows, 8-row groups 1024 B apart
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+constexpr int kMaxStages = 3;
+struct Bars {
+  uint64_t full[kMaxStages], empty[kMaxStages], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+}  // namespace tc
+
+// fp32 router weight [E, H] -> three bf16 planes [3][E][H] with hi + mid + lo == w
+__global__ void __launch_bounds__(256)
+split_router_weight_kernel(const float* __restrict__ wr, size_t n, uint16_t* __restrict__ planes) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint16_t h, m, l;
+  split3(wr[i], h, m, l);
+  planes[i] = h;
+  planes[n + i] = m;
+  planes[2 * n + i] = l;
+}
+
+// grid (ceil(T / 128), n_slices); 192 threads: warp 0 TMA producer, warp 1 MMA issuer (and tensor-
+// memory owner), warps 2-5 epilogue. E a multiple of 16, at most 256; H a multiple of 64.
+// out: [n_slices][T][E] planes (one slice: the logits themselves).
+__global__ void __launch_bounds__(192, 1)
+router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                        float* __restrict__ out, int T, int H, int E, int stages, int* status) {
+  extern __shared__ uint8_t tc_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
+  const int a_bytes = 128 * 128, b_bytes = E * 128;          // one 64-K chunk: token tile, one weight-term tile
+  const int stage_bytes = a_bytes + 3 * b_bytes;
+  tc::Bars* bars = reinterpret_cast<tc::Bars*>(smem + stages * stage_bytes);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+  const int tmem_cols = 2 * E <= 256 ? 256 : 512;            // two accumulators of E columns
+  if (tid == 0) {
+    for (int i = 0; i < tc::kMaxStages; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc::smem_u32(&bars->full[i])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc::smem_u32(&bars->empty[i])));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc::smem_u32(&bars->acc_full)));
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = bars->tmem_base;
+
+  const int t0 = blockIdx.x * 128;
+  const int all_chunks = H / 64;
+  const int ch_begin = (int)blockIdx.y * all_chunks / (int)gridDim.y;
+  const int ch_end = ((int)blockIdx.y + 1) * all_chunks / (int)gridDim.y;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int slot = 0;
+      uint32_t phase = 0;
+      for (int ch = ch_begin; ch < ch_end; ++ch) {
+        if (!tc::wait(tc::smem_u32(&bars->empty[slot]), phase ^ 1u, abort_flag, 31)) break;
+        const uint32_t bar = tc::smem_u32(&bars->full[slot]);
+        const uint32_t dst = tc::smem_u32(smem + slot * stage_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)stage_bytes) : "memory");
+        tc::tma_2d(dst, &map_x, ch * 64, t0, bar);                       // rows past T read as zeros (and still count)
+        for (int term = 0; term < 3; ++term) tc::tma_2d(dst + a_bytes + term * b_bytes, &map_w, ch * 64, term * E, bar);
+        if (++slot == stages) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // bf16 x bf16 -> fp32, both K-major, M = 128, N = E
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(E >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t d_hi = tmem, d_lo = tmem + (uint32_t)E;
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int ch = ch_begin; ch < ch_end; ++ch) {
+        if (!tc::wait(tc::smem_u32(&bars->full[slot]), phase, abort_flag, 32)) {
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t base = tc::smem_u32(smem + slot * stage_bytes);
+        const uint64_t a = tc::desc_sw128(base);
+        const uint64_t b_hi = tc::desc_sw128(base + a_bytes), b_mid = tc::desc_sw128(base + a_bytes + b_bytes),
+                       b_lo = tc::desc_sw128(base + a_bytes + 2 * b_bytes);
+        const uint32_t first = ch != ch_begin ? 1u : 0u;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          tc::mma_ss(d_hi, a + kk * 2, b_hi + kk * 2, idesc, first | (uint32_t)(kk != 0));
+          tc::mma_ss(d_lo, a + kk * 2, b_mid + kk * 2, idesc, first | (uint32_t)(kk != 0));
+          tc::mma_ss(d_lo, a + kk * 2, b_lo + kk * 2, idesc, 1u);
+        }
+        tc::commit(tc::smem_u32(&bars->empty[slot]));
+        if (++slot == stages) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) tc::commit(tc::smem_u32(&bars->acc_full));
+    }
+  } else {
+    // epilogue: warp w reads the lane quarter w % 4; thread = token row
+    const int q = warp & 3;
+    const bool ok = tc::wait(tc::smem_u32(&bars->acc_full), 0, abort_flag, 33);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int t = t0 + q * 32 + lane;
+    float* row = out + ((size_t)blockIdx.y * T + (size_t)(t < T ? t : 0)) * E;
+    if (ok && ch_end > ch_begin) {
+      const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
+      for (int c = 0; c < E; c += 32) {
+        uint32_t hi[32], lo[32];
+        tc::ld32(t_lane + c, hi);
+        tc::ld32(t_lane + E + c, lo);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (t < T) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 v;
+            v.x = __uint_as_float(hi[j]) + __uint_as_float(lo[j]);
+            v.y = __uint_as_float(hi[j + 1]) + __uint_as_float(lo[j + 1]);
+            v.z = __uint_as_float(hi[j + 2]) + __uint_as_float(lo[j + 2]);
+            v.w = __uint_as_float(hi[j + 3]) + __uint_as_float(lo[j + 3]);
+            if (c + j < E) *reinterpret_cast<float4*>(row + c + j) = v;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)tmem_cols) : "memory");
+  }
+  if (tid == 0 && bars->abort_flag != 0 && status != nullptr) atomicExch(status, 100 + bars->abort_flag);
+}
+
 // logits[i] = planes[0][i] + planes[1][i] + ... in plane order (fixed: reproducible)
 __global__ void __launch_bounds__(256)
 sum_planes_kernel(const float* __restrict__ planes, int n_planes, size_t n, float* __restrict__ logits) {
@@ -369,6 +593,48 @@ route_align_small_kernel(const float* __restrict__ logits, const float* __restri
 
 }  // namespace
 
+// moe_gemm_sm100.cu
+CUtensorMap sm100_make_map_bf16(const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_outer);
+int* sm100_status_address();
+
+namespace {
+// VK_MOE_ROUTER=mma keeps prefill-size batches on the mma.sync kernel.
+bool router_tc_mode() {
+  static const bool on = [] {
+    const char* e = std::getenv("VK_MOE_ROUTER");
+    return e == nullptr || std::string(e) != "mma";
+  }();
+  return on;
+}
+
+void launch_router_tc(const uint16_t* x, const float* wr, float* logits, int T, int H, int E, cudaStream_t st) {
+  const int tiles = (T + 127) / 128, chunks = H / 64;
+  int z = std::max(1, std::min(std::min(8, chunks / 4), sm_count() / tiles));
+  const size_t n = (size_t)T * E, n_w = (size_t)E * H;
+  const size_t w_bytes = (3 * n_w * sizeof(uint16_t) + 1023) & ~size_t(1023);
+  uint8_t* ws = static_cast<uint8_t*>(workspace_get(4096 + w_bytes + (z > 1 ? (size_t)z * n * sizeof(float) : 0), st)) + 4096;
+  uint16_t* w_planes = reinterpret_cast<uint16_t*>(ws);
+  float* planes = z > 1 ? reinterpret_cast<float*>(ws + w_bytes) : logits;
+  split_router_weight_kernel<<<(unsigned)((n_w + 255) / 256), 256, 0, st>>>(wr, n_w, w_planes);
+  const int stage_bytes = 128 * 128 + 3 * E * 128;
+  const int stages = std::min(tc::kMaxStages, (227 * 1024 - 2048) / stage_bytes);
+  expects(stages >= 2, "router_logits: expert count too large for the tensor-core kernel");
+  const int smem = stages * stage_bytes + (int)sizeof(tc::Bars) + 1024;
+  static std::atomic<int> configured[64];
+  int dev = 0;
+  VK_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || configured[dev].load() < smem) {
+    VK_CUDA_CHECK(cudaFuncSetAttribute(router_logits_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) configured[dev].store(smem);
+  }
+  const CUtensorMap map_x = sm100_make_map_bf16(x, (uint64_t)H, (uint64_t)T, (uint64_t)H * 2, 128);
+  const CUtensorMap map_w = sm100_make_map_bf16(w_planes, (uint64_t)H, (uint64_t)3 * E, (uint64_t)H * 2, (uint32_t)E);
+  router_logits_tc_kernel<<<dim3((unsigned)tiles, (unsigned)z), 192, smem, st>>>(map_x, map_w, planes, T, H, E, stages,
+                                                                              sm100_status_address());
+  if (z > 1) sum_planes_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(planes, z, n, logits);
+}
+}  // namespace
+
 void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H, int E,
                    void* stream) {
   expects(T >= 0 && H > 0 && E > 0, "router_logits: bad dimensions");
@@ -381,6 +647,8 @@ void router_logits(const uint16_t* x, const float* wr, float* logits, int T, int
     const long long pairs = (long long)T * E;
     router_logits_warp_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, wr, logits, T, H, E);
+  } else if (router_tc_mode() && H % 64 == 0 && E % 16 == 0 && E <= 256 && aligned16) {
+    launch_router_tc(x, wr, logits, T, H, E, static_cast<cudaStream_t>(stream));
   } else if (H % 8 == 0 && aligned16) {
     // the attribute belongs to the device's context: once per device
     static std::atomic<bool> configured_dev[64];
