@@ -159,6 +159,26 @@ def test_routing_indices_bit_exact(name, T):
     _check_route(syn.CONFIGS[name], T)
 
 
+@pytest.mark.parametrize("T,E,H", [(513, 128, 2880), (1000, 48, 512), (640, 256, 1024), (8192, 128, 2880), (700, 16, 64)])
+def test_router_logits_tensor_core_kernel(T, E, H):
+    """Prefill-size router logits (tcgen05; token counts that are no multiple of its 128-token
+    tile, expert counts from one MMA-N granule to the largest tile, one to eight K slices): at
+    least as close to the float64 dot products as the oracle's sequential fp32 sums, and equal
+    from run to run."""
+    cfg = syn.scaled(syn.CONFIGS["c2"], H=H, E=E)
+    r = syn.make_router(cfg, device=DEV)
+    A = syn.make_activations(cfg, T, device=DEV)
+    lg = ops.router_logits(A, r["wr"])
+    lg2 = ops.router_logits(A, r["wr"])
+    torch.cuda.synchronize()
+    ops.kernel_status()
+    assert torch.equal(lg, lg2)
+    exact = A.float().cpu().numpy().astype(np.float64) @ to_np(r["wr"]).astype(np.float64).T
+    ref = oracle.router_logits(bf16_to_u16(A), to_np(r["wr"]))
+    noise = float(np.abs(ref - exact).max())
+    assert float(np.abs(to_np(lg) - exact).max()) <= noise + 2e-6
+
+
 def test_routing_zipf_logits():
     cfg = syn.CONFIGS["c4"]
     _check_route(cfg, 4096, logits=syn.make_zipf_logits(cfg, 4096, device=DEV))
