@@ -178,7 +178,11 @@ int vk_cuda_fused_moe_mxfp4_bf16_prepacked(const uint16_t* A, const uint8_t* w13
 /* Router. The reference has no router in this path; semantics follow its GPU
  * routing ops (src/python/vkernels/torch_ops/tokenspeed_amd/routing.py:58-145,
  * torch_ops/glm_router.py:43-88,184-262).
- * logits[T,E] = bf16 x[T,H] . fp32 wr[E,H]^T, fp32 accumulation. */
+ * logits[T,E] = bf16 x[T,H] . fp32 wr[E,H]^T, fp32 accumulation.
+ * Batches above 512 tokens use the stream's library scratch (the bf16 terms of the router weight
+ * and, when the reduction is cut into slices, one [T,E] plane per slice): at most
+ * 5 KB + 6*E*H + 32*T*E bytes - less than the layer call of the same batch needs, so a stream
+ * reserved for the layer is reserved for its router. */
 int vk_cuda_moe_router_logits(const uint16_t* x, const float* wr, float* logits, int T, int H,
                               int E, void* stream);
 /* sigmoid = 0: softmax scores, selection on score (+ bias), weights = scores,
