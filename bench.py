@@ -307,16 +307,18 @@ def kernel_times(fn, calls):
 GATEUP_DRAM_BYTES = {("c2_gptoss120b_prefill", 8192): 1.503e9}
 
 
-def launches_per_step(T, slots, H=2880):
+def launches_per_step(T, slots, H=2880, E=128):
     """Kernels of this library per layer call: router logits (prefill sizes: weight split, tcgen05
     GEMM, and the sum of its K-slice planes when the batch is cut into slices) + top-k, alignment
-    (1 kernel up to 1024 routed slots, else 3), tile list, row gather, gate/up GEMM, down GEMM."""
+    (1 kernel up to 1024 routed slots, else 3), row gather (which also builds the tile list), gate/up
+    GEMM, down GEMM; small token tiles: row split (+ tile list), gate/up, activation split, down."""
     router = 1
     if T > 512:
         tiles = (T + 127) // 128
         z = max(1, min(8, (H // 64) // 4, torch.cuda.get_device_properties(0).multi_processor_count // tiles))
         router = 2 + (1 if z > 1 else 0)
-    return router + 1 + (1 if T * slots <= 1024 else 3) + 4
+    small_tiles = T <= 256 or T * slots <= 48 * E
+    return router + 1 + (1 if T * slots <= 1024 else 3) + (4 if small_tiles else 3)
 
 
 def decode_sweep(peaks, steps, warmup, prepack=True, parity_tokens=8):
@@ -495,7 +497,7 @@ def run_single_gpu(args, cfg, T):
             "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32", "data": "synthetic",
             "config": workload_config(cfg, T, 1), "roofline": roofline, "parity": parity,
             "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}, "e2e": e2e,
-            "gpu_launches": launches_per_step(T, cfg.slots, cfg.H) * args.steps, "clocks": clocks}
+            "gpu_launches": launches_per_step(T, cfg.slots, cfg.H, cfg.E) * args.steps, "clocks": clocks}
     if args.decode_sweep:
         del layer, w
         torch.cuda.empty_cache()

@@ -1686,30 +1686,36 @@ build_tiles_kernel(const int32_t* __restrict__ expert_ids, int n_blocks, int blo
 }
 
 // A_sorted[r, :] = A[sorted_ids[r] / top_k, :] (or the row at A_rows[sorted_ids[r] / top_k]) for
-// real rows, zeros otherwise.
-__global__ void __launch_bounds__(256)
+// real rows, zeros otherwise: four rows per CTA, 256 threads each. The CTA after the last row
+// CTA builds the token-tile list instead (tiles != nullptr), so that the list costs no launch
+// of its own and is ready when the rows are.
+__global__ void __launch_bounds__(1024)
 gather_rows_kernel(const uint16_t* __restrict__ A, const uint16_t* const* __restrict__ A_rows,
                    const int32_t* __restrict__ sorted_ids,
                    const int32_t* __restrict__ expert_ids, int block_size, int EM, int N, int top_k,
-                   int H, uint16_t* __restrict__ dst, int32_t* __restrict__ inv = nullptr) {
-  const int vec_per_row = H / 8;  // 16-byte vectors
-  const int rows_per_cta = 4;
-  const int r0 = blockIdx.x * rows_per_cta;
-  for (int rr = 0; rr < rows_per_cta; ++rr) {
-    const int r = r0 + rr;
-    if (r >= EM) return;
-    if (expert_ids[r / block_size] < 0) continue;  // never read by any tile
-    const int flat = sorted_ids[r];
-    const bool real = flat >= 0 && flat < N;
-    const int token = real ? flat / top_k : 0;
-    if (real && inv != nullptr && threadIdx.x == 0) inv[flat] = r;
-    // a row address from A_rows may lie in another GPU's memory (peer load over NVLink)
-    const uint4* src = reinterpret_cast<const uint4*>(
-        A_rows != nullptr ? (real ? A_rows[token] : nullptr) : A + (size_t)token * H);
-    uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * H);
-    for (int i = threadIdx.x; i < vec_per_row; i += 256)
-      d[i] = real ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                   int H, uint16_t* __restrict__ dst, int32_t* __restrict__ inv, int max_tok,
+                   TokTile* __restrict__ tiles, int* __restrict__ n_tiles, int max_tiles) {
+  if ((int)blockIdx.x * 4 >= EM) {   // the extra CTA
+    __shared__ int scan[1024];
+    __shared__ int base;
+    if (tiles != nullptr)
+      build_tiles_block<1024>(expert_ids, EM / block_size, block_size, max_tok, tiles, n_tiles, max_tiles, scan, &base);
+    return;
   }
+  const int vec_per_row = H / 8;  // 16-byte vectors
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 8), t = threadIdx.x & 255;
+  if (r >= EM) return;
+  if (expert_ids[r / block_size] < 0) return;  // never read by any tile
+  const int flat = sorted_ids[r];
+  const bool real = flat >= 0 && flat < N;
+  const int token = real ? flat / top_k : 0;
+  if (real && inv != nullptr && t == 0) inv[flat] = r;
+  // a row address from A_rows may lie in another GPU's memory (peer load over NVLink)
+  const uint4* src = reinterpret_cast<const uint4*>(
+      A_rows != nullptr ? (real ? A_rows[token] : nullptr) : A + (size_t)token * H);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * H);
+  for (int i = t; i < vec_per_row; i += 256)
+    d[i] = real ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // Token rows of the fp8 form. Row r of the sorted order (gate/up: the activation row of token
@@ -2391,8 +2397,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
                      "larger batches take the checkpoint-layout weights");
   const bool use_pair = choice.use_pair;
   // a small problem's tile list is built by an extra CTA of the row pre-pass (one launch less)
+  // (and a large one's by an extra CTA of the row gather)
   const bool tiles_in_split = mx && EM / block_size <= 1024;
-  if (!tiles_in_split)
+  if (mx && !tiles_in_split)
     build_tiles_kernel<<<1, 1024, 0, stream>>>(expert_ids, EM / block_size, block_size, max_tok, tiles,
                                                n_tiles, max_tok_tiles(EM));
   uint8_t* x8 = reinterpret_cast<uint8_t*>(gathered);            // fp8 form: pieces of the token rows
@@ -2404,8 +2411,9 @@ void launch_moe_sm100(const uint16_t* A, const uint8_t* w13, const uint8_t* w13_
         A, a_rows, sorted_ids, expert_ids, block_size, EM, M * top_k, top_k, hidden, x8, x8 + (size_t)EM * hidden,
         scale_x, inv, max_tok, tiles_in_split ? tiles : nullptr, n_tiles, max_tok_tiles(EM));
   else
-    gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM,
-                                                         M * top_k, top_k, hidden, gathered, inv);
+    gather_rows_kernel<<<(EM + 3) / 4 + 1, 1024, 0, stream>>>(A, a_rows, sorted_ids, expert_ids, block_size, EM, M * top_k,
+                                                             top_k, hidden, gathered, inv, max_tok, tiles, n_tiles,
+                                                             max_tok_tiles(EM));
 
   GemmParams g{};
   g.sorted_ids = sorted_ids; g.tiles = tiles; g.n_tiles = n_tiles;
@@ -2495,8 +2503,8 @@ void launch_moe_stage_gemm(int which, const uint16_t* rows_in, const uint8_t* w,
                                              n_tiles, max_tok_tiles(EM));
   const uint16_t* token_rows = rows_in;
   if (which == 0) {
-    gather_rows_kernel<<<(EM + 3) / 4, 256, 0, stream>>>(rows_in, nullptr, sorted_ids, expert_ids, block_size, EM,
-                                                         M * top_k, top_k, k_full, gathered);
+    gather_rows_kernel<<<(EM + 3) / 4, 1024, 0, stream>>>(rows_in, nullptr, sorted_ids, expert_ids, block_size, EM,
+                                                          M * top_k, top_k, k_full, gathered, nullptr, 0, nullptr, nullptr, 0);
     token_rows = gathered;
   }
   GemmParams p{};

@@ -458,8 +458,8 @@ class ExpertParallelMoE:
         known = R_recv is not None
         self._stats = {"rows_sent": R_send, "rows_received": R_recv, "tokens_local": T, "form": "peer memory",
                        # router (weight split + GEMM + plane sum at prefill sizes) + top-k, records + counts, barrier,
-                       # unpack, alignment, tiles + gather + two GEMMs, barrier, combine
-                       "launches_per_step": (4 if T > 512 else 2) + 2 + 1 + 1 + (1 if world * cap * slots <= 1024 else 3) + 4 + 1 + 1,
+                       # unpack, alignment, gather (+ tile list) + two GEMMs, barrier, combine
+                       "launches_per_step": (4 if T > 512 else 2) + 2 + 1 + 1 + (1 if world * cap * slots <= 1024 else 3) + 3 + 1 + 1,
                        "dispatch_bytes": R_recv * stride * 4 if known else None, "combine_bytes": 0,
                        "peer_read_bytes": R_recv * H * 2 if known else None,
                        "peer_store_bytes": local_slots * H * 4 if local_slots is not None else None,
